@@ -1,0 +1,305 @@
+// C-ABI entry points of the attention forward: argument checking, tensor-map
+// encoding, variant selection (plain / split-KV / residual) and the small helper
+// kernels around the main one (partial-state combine, bounded-logit operand).
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+
+#include "attn_kernel.cuh"
+#include "host_common.h"
+
+namespace dtb {
+namespace {
+
+constexpr float kLog2e = 1.44269504f;
+constexpr int kNumSms = 148;
+
+// ---------------------------------------------------------------------------
+// Merge `num` partial states per row and write the normalised bf16 output.
+// One warp per query row; lane i owns output columns 4i..4i+3.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ acc_o, const float* __restrict__ acc_m,
+                                                      const float* __restrict__ acc_l, int num, int B, int Hq, int Sq,
+                                                      __nv_bfloat16* __restrict__ o, int64_t osb, int64_t osh,
+                                                      int64_t oss, const int32_t* __restrict__ kv_len, int q_offset,
+                                                      int zero_padded_rows) {
+  const int64_t rows = static_cast<int64_t>(B) * Hq * Sq;
+  const int64_t rid = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (rid >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int s = static_cast<int>(rid % Sq);
+  const int h = static_cast<int>((rid / Sq) % Hq);
+  const int b = static_cast<int>(rid / (static_cast<int64_t>(Sq) * Hq));
+  float m_max = -INFINITY;
+  for (int i = 0; i < num; ++i) {
+    const float l = acc_l[i * rows + rid];
+    const float m = acc_m[i * rows + rid];
+    if (l > 0.f) m_max = fmaxf(m_max, m);
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l_tot = 0.f;
+  for (int i = 0; i < num; ++i) {
+    const float l = acc_l[i * rows + rid];
+    if (!(l > 0.f)) continue;
+    const float w = exp2f(acc_m[i * rows + rid] - m_max);
+    l_tot += l * w;
+    const float4 v = reinterpret_cast<const float4*>(acc_o + (i * rows + rid) * kHeadDim)[lane];
+    acc.x += v.x * w;
+    acc.y += v.y * w;
+    acc.z += v.z * w;
+    acc.w += v.w * w;
+  }
+  const bool padded = zero_padded_rows && kv_len != nullptr && (q_offset + s >= kv_len[b]);
+  const float inv = (l_tot > 0.f && !padded) ? 1.0f / l_tot : 0.f;
+  uint2 packed;
+  packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+  packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+  reinterpret_cast<uint2*>(o + b * osb + h * osh + s * oss)[lane] = packed;
+}
+
+// ---------------------------------------------------------------------------
+// Max L2 row norm per head of a bf16 [B,H,S,128] tensor (one warp per row),
+// folded into norms[h] with an integer atomic max (norms are non-negative).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) row_norm_max_kernel(const __nv_bfloat16* __restrict__ x, int B, int H, int S,
+                                                           int64_t sb, int64_t sh, int64_t ss, float mult,
+                                                           float* __restrict__ norms) {
+  const int64_t rows = static_cast<int64_t>(B) * H * S;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * 8;
+  float best = 0.f;
+  int best_h = -1;
+  for (int64_t rid = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); rid < rows; rid += warps_total) {
+    // rows are visited head-major so one warp mostly stays inside one head
+    const int s = static_cast<int>(rid % S);
+    const int b = static_cast<int>((rid / S) % B);
+    const int h = static_cast<int>(rid / (static_cast<int64_t>(S) * B));
+    if (h != best_h) {
+      if (best_h >= 0 && lane == 0) atomicMax(reinterpret_cast<int*>(norms + best_h), __float_as_int(best));
+      best_h = h;
+      best = 0.f;
+    }
+    const uint2 raw = reinterpret_cast<const uint2*>(x + b * sb + h * sh + s * ss)[lane];
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    float ss2 = a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss2 += __shfl_xor_sync(0xffffffffu, ss2, o);
+    best = fmaxf(best, sqrtf(ss2) * mult);
+  }
+  if (best_h >= 0 && lane == 0) atomicMax(reinterpret_cast<int*>(norms + best_h), __float_as_int(best));
+}
+
+__global__ void fixed_m_finish_kernel(const float* __restrict__ norms, int Hq, int Hkv, float gate,
+                                      float* __restrict__ mk) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= Hq) return;
+  const float bound = norms[h] * norms[Hq + h / (Hq / Hkv)];
+  mk[h] = ceilf(bound);
+  mk[Hq + h] = (bound <= gate) ? 1.0f : 0.0f;
+}
+
+// ---------------------------------------------------------------------------
+int check_params(const dtb_attn_params* p, bool need_o) {
+  if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr) return DTB_ERR_NULL;
+  if (need_o && p->o == nullptr) return DTB_ERR_NULL;
+  if (p->D != kHeadDim) return DTB_ERR_SHAPE;
+  if (p->B <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->Sq <= 0 || p->Skv <= 0) return DTB_ERR_SHAPE;
+  if (p->Hq % p->Hkv != 0) return DTB_ERR_SHAPE;
+  if (p->Hq > 65535 || static_cast<int64_t>(p->B) * 64 > 65535) return DTB_ERR_SHAPE;
+  if (need_o) {
+    if (reinterpret_cast<uintptr_t>(p->o) & 15u) return DTB_ERR_ALIGN;
+    if ((p->o_stride_s * 2) & 15 || (p->o_stride_h * 2) & 15 || (p->o_stride_b * 2) & 15) return DTB_ERR_ALIGN;
+  }
+  if ((p->flags & DTB_FLAG_BOUNDED_LOGITS) && p->mk == nullptr) return DTB_ERR_NULL;
+  return DTB_OK;
+}
+
+int q_blocks(const dtb_attn_params* p) { return (p->Sq + kQTiles * kBlockM - 1) / (kQTiles * kBlockM); }
+
+// Split-KV factor.  Splitting pays when the (batch, head, query-block) grid leaves
+// most SMs idle and each CTA would otherwise sweep many key tiles alone.
+int resolve_splits(const dtb_attn_params* p) {
+  if (p->num_splits == 1) return 1;
+  const int kv_tiles = (p->Skv + kBlockN - 1) / kBlockN;
+  int n = p->num_splits;
+  if (n <= 0) {
+    const int64_t ctas = static_cast<int64_t>(q_blocks(p)) * p->Hq * p->B;
+    if (ctas * 2 > kNumSms || kv_tiles < 8) return 1;
+    n = static_cast<int>(kNumSms / ctas);
+    n = std::min(n, kv_tiles / 4);
+  }
+  n = std::min(n, std::min(kv_tiles, 64));
+  return std::max(n, 1);
+}
+
+size_t split_workspace_bytes(const dtb_attn_params* p, int splits) {
+  const size_t rows = static_cast<size_t>(splits) * p->B * p->Hq * p->Sq;
+  return rows * (kHeadDim + 2) * sizeof(float);
+}
+
+// The opt-in shared-memory size is a per-device function attribute: set it the first
+// time each device is used (an immutable cache; nothing else in the library is global).
+std::atomic<bool> g_attrs_set[64];
+
+cudaError_t ensure_kernel_attrs() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && g_attrs_set[dev].load(std::memory_order_acquire)) return cudaSuccess;
+  e = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kSmemBytes));
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kSmemBytes));
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64) g_attrs_set[dev].store(true, std::memory_order_release);
+  return cudaSuccess;
+}
+
+int fill_kernel_params(const dtb_attn_params* p, AttnKernelParams* kp) {
+  int st = make_tmap_bhsd(&kp->tmap_q, p->q, p->B, p->Hq, p->Sq, p->q_stride_b, p->q_stride_h, p->q_stride_s,
+                          kBlockM);
+  if (st != DTB_OK) return st;
+  st = make_tmap_bhsd(&kp->tmap_k, p->k, p->B, p->Hkv, p->Skv, p->k_stride_b, p->k_stride_h, p->k_stride_s,
+                      kBlockN);
+  if (st != DTB_OK) return st;
+  st = make_tmap_bhsd(&kp->tmap_v, p->v, p->B, p->Hkv, p->Skv, p->v_stride_b, p->v_stride_h, p->v_stride_s,
+                      kBlockN);
+  if (st != DTB_OK) return st;
+  kp->o = static_cast<__nv_bfloat16*>(p->o);
+  kp->o_stride_b = p->o_stride_b;
+  kp->o_stride_h = p->o_stride_h;
+  kp->o_stride_s = p->o_stride_s;
+  kp->acc_o = kp->acc_m = kp->acc_l = nullptr;
+  kp->kv_len = p->kv_len;
+  kp->mk = (p->flags & DTB_FLAG_BOUNDED_LOGITS) ? p->mk : nullptr;
+  kp->status = p->status;
+  kp->B = p->B;
+  kp->Hq = p->Hq;
+  kp->Hkv = p->Hkv;
+  kp->Sq = p->Sq;
+  kp->Skv = p->Skv;
+  kp->kv_offset = 0;
+  kp->q_offset = 0;
+  kp->num_splits = 1;
+  kp->acc_init = 1;
+  kp->zero_padded_rows = (p->flags & DTB_FLAG_ZERO_PADDED_ROWS) ? 1 : 0;
+  const float scale = p->scale > 0.f ? p->scale : 1.0f / sqrtf(static_cast<float>(p->D));
+  kp->scale_log2 = scale * kLog2e;
+  return DTB_OK;
+}
+
+}  // namespace
+}  // namespace dtb
+
+using namespace dtb;
+
+extern "C" int dtb_attn_supported(const dtb_attn_params* p, int* why) {
+  int st = check_params(p, true);
+  if (st == DTB_OK && !device_is_sm100()) st = DTB_ERR_ARCH;
+  if (why != nullptr) *why = st;
+  return st == DTB_OK ? 1 : 0;
+}
+
+extern "C" size_t dtb_attn_workspace_bytes(const dtb_attn_params* p) {
+  if (check_params(p, false) != DTB_OK) return 0;
+  const int splits = resolve_splits(p);
+  return splits > 1 ? split_workspace_bytes(p, splits) : 0;
+}
+
+extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = check_params(p, true);
+  if (st != DTB_OK) return st;
+  if (!device_is_sm100()) return DTB_ERR_ARCH;
+  if (ensure_kernel_attrs() != cudaSuccess) return DTB_ERR_LAUNCH;
+  AttnKernelParams kp;
+  st = fill_kernel_params(p, &kp);
+  if (st != DTB_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  int splits = resolve_splits(p);
+  if (splits > 1) {
+    const size_t need = split_workspace_bytes(p, splits);
+    if (workspace == nullptr || workspace_bytes < need) {
+      if (p->num_splits > 1) return DTB_ERR_WORKSPACE;  // explicitly requested: refuse
+      splits = 1;                                       // automatic: run unsplit
+    }
+  }
+  const dim3 block(kNumThreads);
+  if (splits == 1) {
+    const dim3 grid(q_blocks(p), p->Hq, p->B);
+    attn_fwd_kernel<false><<<grid, block, kSmemBytes, s>>>(kp);
+    return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+  }
+  const size_t rows = static_cast<size_t>(splits) * p->B * p->Hq * p->Sq;
+  kp.acc_o = static_cast<float*>(workspace);
+  kp.acc_m = kp.acc_o + rows * kHeadDim;
+  kp.acc_l = kp.acc_m + rows;
+  kp.num_splits = splits;
+  kp.acc_init = 1;
+  const dim3 grid(q_blocks(p), p->Hq, p->B * splits);
+  attn_fwd_kernel<true><<<grid, block, kSmemBytes, s>>>(kp);
+  if (cudaGetLastError() != cudaSuccess) return DTB_ERR_LAUNCH;
+  const int64_t out_rows = static_cast<int64_t>(p->B) * p->Hq * p->Sq;
+  combine_kernel<<<static_cast<unsigned>((out_rows + 7) / 8), 256, 0, s>>>(
+      kp.acc_o, kp.acc_m, kp.acc_l, splits, p->B, p->Hq, p->Sq, kp.o, kp.o_stride_b, kp.o_stride_h, kp.o_stride_s,
+      p->kv_len, 0, kp.zero_padded_rows);
+  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+}
+
+extern "C" int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_residual* r, void* stream) {
+  int st = check_params(p, false);
+  if (st != DTB_OK) return st;
+  if (r == nullptr || r->o_acc == nullptr || r->m == nullptr || r->l == nullptr) return DTB_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(r->o_acc) & 15u) return DTB_ERR_ALIGN;
+  if (!device_is_sm100()) return DTB_ERR_ARCH;
+  if (ensure_kernel_attrs() != cudaSuccess) return DTB_ERR_LAUNCH;
+  AttnKernelParams kp;
+  st = fill_kernel_params(p, &kp);
+  if (st != DTB_OK) return st;
+  kp.acc_o = r->o_acc;
+  kp.acc_m = r->m;
+  kp.acc_l = r->l;
+  kp.kv_offset = r->kv_offset;
+  kp.q_offset = r->q_offset;
+  kp.acc_init = r->init ? 1 : 0;
+  kp.zero_padded_rows = 0;  // padded rows are zeroed by dtb_attn_finalize
+  const dim3 grid(q_blocks(p), p->Hq, p->B);
+  attn_fwd_kernel<true><<<grid, dim3(kNumThreads), kSmemBytes, static_cast<cudaStream_t>(stream)>>>(kp);
+  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+}
+
+extern "C" int dtb_attn_finalize(const dtb_attn_params* p, const dtb_attn_residual* r, void* stream) {
+  if (p == nullptr || p->o == nullptr || r == nullptr || r->o_acc == nullptr || r->m == nullptr || r->l == nullptr)
+    return DTB_ERR_NULL;
+  if (p->D != kHeadDim || p->B <= 0 || p->Hq <= 0 || p->Sq <= 0) return DTB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(p->o) & 7u) || (p->o_stride_s & 3) || (p->o_stride_h & 3) || (p->o_stride_b & 3))
+    return DTB_ERR_ALIGN;
+  const int64_t out_rows = static_cast<int64_t>(p->B) * p->Hq * p->Sq;
+  combine_kernel<<<static_cast<unsigned>((out_rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      r->o_acc, r->m, r->l, 1, p->B, p->Hq, p->Sq, static_cast<__nv_bfloat16*>(p->o), p->o_stride_b, p->o_stride_h,
+      p->o_stride_s, p->kv_len, r->q_offset, (p->flags & DTB_FLAG_ZERO_PADDED_ROWS) ? 1 : 0);
+  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+}
+
+extern "C" int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float* norms, float* mk_out, void* stream) {
+  int st = check_params(p, false);
+  if (st != DTB_OK) return st;
+  if (norms == nullptr || mk_out == nullptr) return DTB_ERR_NULL;
+  if ((reinterpret_cast<uintptr_t>(p->q) & 7u) || (reinterpret_cast<uintptr_t>(p->k) & 7u)) return DTB_ERR_ALIGN;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(norms, 0, sizeof(float) * (p->Hq + p->Hkv), s) != cudaSuccess) return DTB_ERR_LAUNCH;
+  const float scale = p->scale > 0.f ? p->scale : 1.0f / sqrtf(static_cast<float>(p->D));
+  // The reference takes the norm of the bf16-rounded product q * scale * log2(e); this kernel
+  // applies the scale in f32 after the MMA, so the norm of the unrounded product is the exact bound.
+  auto blocks = [](int64_t rows) { return static_cast<unsigned>(std::min<int64_t>((rows + 7) / 8, 148 * 16)); };
+  row_norm_max_kernel<<<blocks(static_cast<int64_t>(p->B) * p->Hq * p->Sq), 256, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(p->q), p->B, p->Hq, p->Sq, p->q_stride_b, p->q_stride_h, p->q_stride_s,
+      scale * kLog2e, norms);
+  row_norm_max_kernel<<<blocks(static_cast<int64_t>(p->B) * p->Hkv * p->Skv), 256, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(p->k), p->B, p->Hkv, p->Skv, p->k_stride_b, p->k_stride_h, p->k_stride_s, 1.0f,
+      norms + p->Hq);
+  fixed_m_finish_kernel<<<(p->Hq + 127) / 128, 128, 0, s>>>(norms, p->Hq, p->Hkv, gate, mk_out);
+  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+}

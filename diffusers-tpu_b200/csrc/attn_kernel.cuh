@@ -1,0 +1,497 @@
+// Joint-attention forward for sm_100a: one CTA owns 256 query rows (two 128-row
+// tiles) of one (batch, head) and sweeps the valid keys in 128-key tiles.
+//
+// Warp roles (320 threads):
+//   warps 0-3   softmax group 0: one thread per query row of tile 0
+//   warps 4-7   softmax group 1: one thread per query row of tile 1
+//   warp  8     MMA issuer (lane 0 issues tcgen05.mma; the warp stays converged)
+//   warp  9     TMA producer (lane 0 issues the tensor loads)
+//
+// Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 f32 columns each.  P (bf16)
+// is written over the first 64 columns of its S tile and consumed from tensor
+// memory by the PV MMA, so probabilities never touch shared memory.
+//
+// Shared memory: Q (2 x 32 KB, loaded once) and a ring of 32 KB slots through
+// which K_0, V_0, K_1, V_1, ... flow; every tile is two 64-column panels written
+// by TMA with the 128-byte swizzle the MMA descriptors expect.
+//
+// The two softmax groups ping-pong: while group 0 exponentiates S0 the tensor
+// core runs P1*V and the next Q1*K^T, and vice versa.  MMAs issued by one thread
+// execute in order, which is what makes the S/P aliasing and the O rescale safe:
+//   * S_t(j+1) = Q_t K_{j+1}^T is issued after O_t += P_t(j) V_j, so it cannot
+//     overwrite P_t(j) early;
+//   * the commit that publishes S_t(j) follows PV_t(j-1) in issue order, so a
+//     softmax thread that has seen S_t(j) may read-modify-write O_t.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace dtb {
+
+constexpr int kBlockM = 128;                 // query rows per tile
+constexpr int kQTiles = 2;                   // query tiles per CTA
+constexpr int kBlockN = 128;                 // keys per tile
+constexpr int kHeadDim = 128;
+constexpr int kStages = 4;                   // K/V ring slots
+constexpr uint32_t kPanelBytes = 128 * 64 * 2;
+constexpr uint32_t kTileBytes = 2 * kPanelBytes;
+constexpr int kNumSoftmaxThreads = kQTiles * kBlockM;
+constexpr int kMmaWarp = kNumSoftmaxThreads / 32;
+constexpr int kLoadWarp = kMmaWarp + 1;
+constexpr int kNumThreads = kNumSoftmaxThreads + 64;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;    // log2 units: rescale O only when the row max grew by > 2^8
+constexpr float kFixedMRecenter = 88.0f;     // bounded-logit mode exponent offset (m - 88)
+
+struct __align__(8) PipelineBarriers {
+  uint64_t q_full[kQTiles];
+  uint64_t kv_full[kStages];
+  uint64_t kv_empty[kStages];
+  uint64_t s_full[kQTiles];
+  uint64_t p_full[kQTiles];
+  uint64_t o_full[kQTiles];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t kSmemBytes = 1024 /* alignment slack */ + kQTiles * kTileBytes + kStages * kTileBytes +
+                              sizeof(PipelineBarriers);
+
+// Barrier-site ids reported in status[1] when a wait runs out.
+enum WaitSite : int {
+  SITE_Q_FULL = 10, SITE_KV_FULL = 20, SITE_KV_EMPTY = 30, SITE_S_FULL = 40, SITE_P_FULL = 50, SITE_O_FULL = 60
+};
+
+struct AttnKernelParams {
+  CUtensorMap tmap_q, tmap_k, tmap_v;
+  __nv_bfloat16* o;           // normalised output (normal mode)
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  float* acc_o;               // residual / partial mode: f32 [units, B, Hq, Sq, D]
+  float* acc_m;               //                          f32 [units, B, Hq, Sq]
+  float* acc_l;
+  const int32_t* kv_len;      // [B] or null
+  const float* mk;            // [2, Hq] or null
+  int32_t* status;
+  int B, Hq, Hkv, Sq, Skv;
+  int kv_offset;              // global index of key 0 of this call (ring shards)
+  int q_offset;               // global index of query row 0 of this call
+  int num_splits;             // >= 1
+  int acc_init;               // residual mode: start from the empty state
+  int zero_padded_rows;
+  float scale_log2;           // softmax scale * log2(e)
+};
+
+// Warp-uniform bounded wait: every lane polls, and the warp agrees on the outcome so
+// that warp-collective instructions after it are never reached by a partial warp.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, int site) {
+  return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, ctx, site));
+}
+
+// ---------------------------------------------------------------------------
+// One key tile of online softmax for the row owned by this thread.
+// ---------------------------------------------------------------------------
+template <bool kFixedM>
+__device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, float scale_log2, int valid_cols,
+                                             bool o_live, float& m_used, float& l_sum) {
+  float s[kBlockN];
+  {
+    uint32_t r[32];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      tmem_ld32(s_tmem + c * 32, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
+    }
+  }
+  if (valid_cols < kBlockN) {
+#pragma unroll
+    for (int i = 0; i < kBlockN; ++i)
+      if (i >= valid_cols) s[i] = -INFINITY;
+  }
+  if (!kFixedM) {
+    float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+#pragma unroll
+    for (int i = 4; i < kBlockN; i += 4) {
+      mx0 = fmaxf(mx0, s[i]);
+      mx1 = fmaxf(mx1, s[i + 1]);
+      mx2 = fmaxf(mx2, s[i + 2]);
+      mx3 = fmaxf(mx3, s[i + 3]);
+    }
+    const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+    const bool grow = mx > m_used + kRescaleThreshold;  // always true while m_used == -inf
+    if (o_live && __any_sync(0xffffffffu, grow)) {
+      const float alpha = grow ? ex2(m_used - mx) : 1.0f;
+      l_sum *= alpha;
+      uint32_t r[32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld32(o_tmem + c * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+        tmem_st32(o_tmem + c * 32, r);
+      }
+    } else if (grow) {
+      // No accumulator yet: only the running sum carries history (it is 0 or, in
+      // residual mode with an empty incoming state, already 0).
+      l_sum *= ex2(m_used - mx);
+    }
+    if (grow) m_used = mx;
+  }
+  const float neg_m = -m_used;
+  float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float p0 = ex2(fmaf(s[c * 32 + 2 * i], scale_log2, neg_m));
+      const float p1 = ex2(fmaf(s[c * 32 + 2 * i + 1], scale_log2, neg_m));
+      acc0 += p0;
+      acc1 += p1;
+      pk[i] = pack_bf16x2(p0, p1);
+    }
+    tmem_st16(s_tmem + c * 16, pk);
+  }
+  l_sum += acc0 + acc1;
+  tmem_wait_st();
+}
+
+// ---------------------------------------------------------------------------
+// The kernel.  kResidual = false: write the normalised bf16 output.
+//              kResidual = true : fold into / emit the running (o, m, l) state
+//                                 (ring steps and split-KV partials).
+// ---------------------------------------------------------------------------
+template <bool kResidual>
+__global__ void __maxnreg__(200) attn_fwd_kernel(const __grid_constant__ AttnKernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem;
+  {
+    const uint32_t a = smem_u32(smem_raw);
+    smem = smem_raw + (((a + 1023u) & ~1023u) - a);
+  }
+  uint8_t* smem_q = smem;
+  uint8_t* smem_kv = smem + kQTiles * kTileBytes;
+  PipelineBarriers* bars = reinterpret_cast<PipelineBarriers*>(smem_kv + kStages * kTileBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int split = blockIdx.z % p.num_splits;
+  const int b = blockIdx.z / p.num_splits;
+  const int h = blockIdx.y;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = blockIdx.x * (kQTiles * kBlockM);
+
+  // Valid keys of this call: global indices [kv_offset, kv_offset + Skv) below kv_len[b].
+  const int kv_len_b = (p.kv_len != nullptr) ? max(p.kv_len[b], 0) : 0x7fffffff;
+  const int kv_eff = max(min(kv_len_b - p.kv_offset, p.Skv), 0);
+  const int n_total = (kv_eff + kBlockN - 1) / kBlockN;
+  const int per_split = (n_total + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = min(split * per_split, n_total);
+  const int tile_end = min(tile_begin + per_split, n_total);
+  const int n_tiles = tile_end - tile_begin;
+  const bool block_padded = p.zero_padded_rows && (p.q_offset + q0 >= kv_len_b);
+
+  const int64_t unit = kResidual ? ((static_cast<int64_t>(split) * p.B + b) * p.Hq + h) : 0;
+
+  if (n_tiles <= 0 || block_padded) {
+    // Nothing to attend to: emit zeros (normal) or the empty state (residual, when initialising).
+    if (threadIdx.x < kNumSoftmaxThreads) {
+      const int row = q0 + threadIdx.x;
+      if (row < p.Sq) {
+        if (!kResidual) {
+          uint4* dst = reinterpret_cast<uint4*>(p.o + b * p.o_stride_b + h * p.o_stride_h + row * p.o_stride_s);
+#pragma unroll
+          for (int i = 0; i < kHeadDim * 2 / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+        } else if (p.acc_init) {
+          float4* dst = reinterpret_cast<float4*>(p.acc_o + (unit * p.Sq + row) * kHeadDim);
+#pragma unroll
+          for (int i = 0; i < kHeadDim / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          p.acc_m[unit * p.Sq + row] = -INFINITY;
+          p.acc_l[unit * p.Sq + row] = 0.f;
+        }
+      }
+    }
+    return;
+  }
+
+  AbortCtx ctx{&bars->abort_flag, p.status};
+
+  if (threadIdx.x == kMmaWarp * 32) {
+    bars->abort_flag = 0;
+    for (int i = 0; i < kQTiles; ++i) {
+      mbar_init(smem_u32(&bars->q_full[i]), 1);
+      mbar_init(smem_u32(&bars->s_full[i]), 1);
+      mbar_init(smem_u32(&bars->p_full[i]), kBlockM);
+      mbar_init(smem_u32(&bars->o_full[i]), 1);
+    }
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(smem_u32(&bars->kv_full[i]), 1);
+      mbar_init(smem_u32(&bars->kv_empty[i]), 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == kLoadWarp && lane == 0) {
+    tma_prefetch_desc(&p.tmap_q);
+    tma_prefetch_desc(&p.tmap_k);
+    tma_prefetch_desc(&p.tmap_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == kLoadWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    bool ok = true;
+    if (lane == 0) {
+      for (int t = 0; t < kQTiles; ++t) {
+        const uint32_t bar = smem_u32(&bars->q_full[t]);
+        mbar_expect_tx(bar, kTileBytes);
+        const uint32_t dst = smem_u32(smem_q + t * kTileBytes);
+        tma_load_4d(dst, &p.tmap_q, bar, 0, q0 + t * kBlockM, h, b);
+        tma_load_4d(dst + kPanelBytes, &p.tmap_q, bar, 64, q0 + t * kBlockM, h, b);
+      }
+      for (int i = 0; i < 2 * n_tiles && ok; ++i) {
+        const int slot = i % kStages;
+        const int use = i / kStages;
+        if (use > 0) ok = mbar_wait(smem_u32(&bars->kv_empty[slot]), (use - 1) & 1, ctx, SITE_KV_EMPTY + slot);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&bars->kv_full[slot]);
+        mbar_expect_tx(bar, kTileBytes);
+        const uint32_t dst = smem_u32(smem_kv + slot * kTileBytes);
+        const int row = (tile_begin + (i >> 1)) * kBlockN;
+        const CUtensorMap* tm = (i & 1) ? &p.tmap_v : &p.tmap_k;
+        tma_load_4d(dst, tm, bar, 0, row, hk, b);
+        tma_load_4d(dst + kPanelBytes, tm, bar, 64, row, hk, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBlockN, false, false);
+    constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, kHeadDim, false, true);
+    const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(smem_q), 16, 1024);
+    const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem_kv), 16, 1024);
+    const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem_kv), kPanelBytes, 1024);
+    bool ok = true;
+
+    auto issue_qk = [&](int t, int slot) {
+      if (lane == 0) {
+        const uint64_t a0 = q_desc0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
+        const uint64_t b0 = k_desc0 + static_cast<uint64_t>((slot * kTileBytes) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+          const uint64_t off = static_cast<uint64_t>(((kk & 3) * 32 + (kk >> 2) * kPanelBytes) >> 4);
+          mma_ss(tmem_base + t * kBlockN, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(smem_u32(&bars->s_full[t]));
+      }
+      __syncwarp();
+    };
+    auto issue_pv = [&](int t, int slot, bool accumulate) {
+      if (lane == 0) {
+        const uint64_t b0 = v_desc0 + static_cast<uint64_t>((slot * kTileBytes) >> 4);
+        const uint32_t d_tmem = tmem_base + (kQTiles + t) * kBlockN;
+        const uint32_t a_tmem = tmem_base + t * kBlockN;
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          const uint64_t off = static_cast<uint64_t>((kk * 16 * 128) >> 4);
+          mma_ts(d_tmem, a_tmem + kk * 8, b0 + off, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+        }
+      }
+      __syncwarp();
+    };
+    auto commit_to = [&](uint64_t* bar) {
+      if (lane == 0) mma_commit(smem_u32(bar));
+      __syncwarp();
+    };
+    auto wait_kv = [&](int i) {
+      const int slot = i % kStages;
+      return warp_wait(&bars->kv_full[slot], (i / kStages) & 1, ctx, SITE_KV_FULL + slot);
+    };
+
+    // Prologue: S_t(0) = Q_t K_0^T for both tiles.
+    ok = warp_wait(&bars->q_full[0], 0, ctx, SITE_Q_FULL);
+    if (ok) ok = wait_kv(0);
+    if (ok) {
+      tc_fence_after();
+      issue_qk(0, 0);
+      ok = warp_wait(&bars->q_full[1], 0, ctx, SITE_Q_FULL + 1);
+    }
+    if (ok) {
+      tc_fence_after();
+      issue_qk(1, 0);
+      commit_to(&bars->kv_empty[0]);
+    }
+    const bool o_preloaded = kResidual && !p.acc_init;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int iv = 2 * j + 1;
+      const int ik = 2 * j + 2;
+      ok = wait_kv(iv);
+      for (int t = 0; t < kQTiles && ok; ++t) {
+        ok = warp_wait(&bars->p_full[t], j & 1, ctx, SITE_P_FULL + t);
+        if (!ok) break;
+        tc_fence_after();
+        issue_pv(t, iv % kStages, j > 0 || o_preloaded);
+        if (t == kQTiles - 1) commit_to(&bars->kv_empty[iv % kStages]);
+        if (j + 1 < n_tiles) {
+          if (t == 0) {
+            ok = wait_kv(ik);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          issue_qk(t, ik % kStages);
+          if (t == kQTiles - 1) commit_to(&bars->kv_empty[ik % kStages]);
+        } else {
+          commit_to(&bars->o_full[t]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int t = warp >> 2;                       // query tile of this group
+    const int row_in_tile = threadIdx.x & (kBlockM - 1);
+    const int row = q0 + t * kBlockM + row_in_tile;  // query row within this call
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_off + t * kBlockN;
+    const uint32_t o_tmem = tmem_base + lane_off + (kQTiles + t) * kBlockN;
+    const float scale_log2 = p.scale_log2;
+    const bool row_in_range = row < p.Sq;
+    const int64_t acc_row = unit * p.Sq + row;
+
+    float m_used = -INFINITY;
+    float l_sum = 0.f;
+    bool fixed_m = false;
+    if (p.mk != nullptr && p.mk[p.Hq + h] > 0.5f) {
+      fixed_m = true;
+      m_used = p.mk[h] - kFixedMRecenter;
+    }
+    bool o_live = false;
+    if (kResidual && !p.acc_init) {
+      // Bring the running state of this row into registers / tensor memory.
+      float m_in = -INFINITY, l_in = 0.f;
+      if (row_in_range) {
+        m_in = p.acc_m[acc_row];
+        l_in = p.acc_l[acc_row];
+      }
+      const float4* src = reinterpret_cast<const float4*>(p.acc_o + acc_row * kHeadDim);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float4 v = row_in_range ? src[c * 8 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+          r[4 * i] = __float_as_uint(v.x);
+          r[4 * i + 1] = __float_as_uint(v.y);
+          r[4 * i + 2] = __float_as_uint(v.z);
+          r[4 * i + 3] = __float_as_uint(v.w);
+        }
+        tmem_st32(o_tmem + c * 32, r);
+      }
+      tmem_wait_st();
+      o_live = true;
+      if (fixed_m) {
+        // The incoming state is expressed relative to m_in; re-express it relative to the fixed offset.
+        // (Callers that use the bounded-logit mode keep one offset for the whole ring, so this is a no-op.)
+        const bool shift = (m_in != m_used) && (l_in > 0.f);
+        if (__any_sync(0xffffffffu, shift)) {
+          const float alpha = shift ? ex2(m_in - m_used) : 1.0f;
+          l_in *= alpha;
+          uint32_t r[32];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld32(o_tmem + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(o_tmem + c * 32, r);
+          }
+          tmem_wait_st();
+        }
+      } else {
+        m_used = m_in;
+      }
+      l_sum = l_in;
+    }
+
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      ok = warp_wait(&bars->s_full[t], j & 1, ctx, SITE_S_FULL + t);
+      if (!ok) break;
+      tc_fence_after();
+      const int valid_cols = min(kv_eff - (tile_begin + j) * kBlockN, kBlockN);
+      if (fixed_m) {
+        softmax_tile<true>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum);
+      } else {
+        softmax_tile<false>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum);
+      }
+      o_live = true;
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars->p_full[t]));
+    }
+    if (ok) ok = warp_wait(&bars->o_full[t], 0, ctx, SITE_O_FULL + t);
+    if (ok) {
+      tc_fence_after();
+      if (kResidual) {
+        float4* dst = reinterpret_cast<float4*>(p.acc_o + acc_row * kHeadDim);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(o_tmem + c * 32, r);
+          tmem_wait_ld();
+          if (row_in_range) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[c * 8 + i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                           __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+          }
+        }
+        if (row_in_range) {
+          p.acc_m[acc_row] = m_used;
+          p.acc_l[acc_row] = l_sum;
+        }
+      } else {
+        const bool padded = p.zero_padded_rows && (p.q_offset + row >= kv_len_b);
+        const float inv = (l_sum > 0.f && !padded) ? (1.0f / l_sum) : 0.f;
+        uint4* dst = reinterpret_cast<uint4*>(p.o + b * p.o_stride_b + h * p.o_stride_h + row * p.o_stride_s);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(o_tmem + c * 32, r);
+          tmem_wait_ld();
+          if (row_in_range) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+              dst[c * 4 + i] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (bars->abort_flag) {
+    // Give copies and MMAs that are still in flight time to land before the
+    // shared and tensor memory they target is released.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace dtb

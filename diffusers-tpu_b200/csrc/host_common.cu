@@ -1,0 +1,71 @@
+#include "host_common.h"
+
+#include <mutex>
+
+namespace dtb {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
+    (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb,
+                   int64_t sh, int64_t ss, int box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return DTB_ERR_LAUNCH;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return DTB_ERR_ALIGN;
+  const int64_t esz = 2;
+  if (((ss * esz) & 15) || ((sh * esz) & 15) || ((sb * esz) & 15)) return DTB_ERR_ALIGN;
+  if (ss <= 0 || sh < 0 || sb < 0) return DTB_ERR_SHAPE;
+  cuuint64_t gdim[4] = {128, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
+                        static_cast<cuuint64_t>(B)};
+  // A size-1 axis may come with any stride (torch reports arbitrary values there);
+  // give it a harmless legal one.
+  cuuint64_t gstr[3] = {static_cast<cuuint64_t>(ss * esz),
+                        static_cast<cuuint64_t>((H > 1 ? sh : S * ss) * esz),
+                        static_cast<cuuint64_t>((B > 1 ? sb : H * S * ss) * esz)};
+  for (int i = 0; i < 3; ++i)
+    if (gstr[i] == 0 || (gstr[i] & 15)) gstr[i] = 256;  // only reachable for size-1 axes
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DTB_OK : DTB_ERR_LAUNCH;
+}
+
+bool device_is_sm100() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
+  return major == 10;
+}
+
+}  // namespace dtb
+
+extern "C" int dtb_version(void) { return 100; }
+
+extern "C" const char* dtb_status_string(int status) {
+  switch (status) {
+    case DTB_OK: return "ok";
+    case DTB_ERR_NULL: return "a required pointer is NULL";
+    case DTB_ERR_DTYPE: return "unsupported element type";
+    case DTB_ERR_SHAPE: return "unsupported shape";
+    case DTB_ERR_ALIGN: return "pointer or stride is not 16-byte aligned";
+    case DTB_ERR_ARCH: return "device is not sm_100";
+    case DTB_ERR_WORKSPACE: return "workspace missing or too small";
+    case DTB_ERR_LAUNCH: return "CUDA error while encoding tensor maps or launching";
+    case DTB_ERR_TIMEOUT: return "a bounded device wait ran out";
+    case DTB_ERR_UNSUPPORTED: return "unsupported option";
+    default: return "unknown status";
+  }
+}

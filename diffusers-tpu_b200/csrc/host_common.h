@@ -1,0 +1,31 @@
+// Host-side helpers shared by the C-ABI translation units: status mapping, the
+// driver entry point for tensor-map encoding, and the [B,H,S,D] bf16 tensor map.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/dtb200_attn.h"
+
+namespace dtb {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+// Resolved once; the driver symbol is reached through the runtime so the library
+// does not link against libcuda directly.
+EncodeTiledFn get_encode_tiled();
+
+// Tensor map over a bf16 [B, H, S, 128] tensor with element strides (sb, sh, ss, 1):
+// boxes of 64 (head_dim) x `box_rows` (sequence) elements, 128-byte swizzle, zero fill
+// outside the tensor.  Returns a dtb_status.
+int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb,
+                   int64_t sh, int64_t ss, int box_rows);
+
+// True when the current device is compute capability 10.x.
+bool device_is_sm100();
+
+}  // namespace dtb

@@ -1,0 +1,23 @@
+"""dtb200 — B200-native joint (text + image/video token) attention forward for DiT blocks.
+
+A drop-in for the device-local attention entry points of shungcp/diffusers-tpu
+(``diffusers_tpu.kernels.splash.attention`` / ``residual_attention`` and the SDPA callable of
+``diffusers_tpu.kernels.mesh_attention``), backed by hand-written sm_100a kernels behind a C ABI.
+"""
+from .ops import (  # noqa: F401
+    FIXED_M_RING_SAFE_BOUND,
+    FIXED_M_SAFE_BOUND,
+    ResidualState,
+    attention,
+    check_device_status,
+    finalize_residual,
+    fixed_m_operands,
+    residual_attention,
+    residual_attention_,
+    sdpa,
+)
+
+__all__ = [
+    "attention", "residual_attention", "residual_attention_", "finalize_residual", "fixed_m_operands",
+    "sdpa", "ResidualState", "check_device_status", "FIXED_M_SAFE_BOUND", "FIXED_M_RING_SAFE_BOUND",
+]

@@ -1,0 +1,119 @@
+"""ctypes binding of ``libdtb200_attn.so`` (the C ABI declared in ``include/dtb200_attn.h``).
+
+The library is the only compute path: if it is missing and cannot be built, or a call
+returns a non-zero status, an exception is raised.  There is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+from . import build as _build
+
+DTB_OK = 0
+STATUS_NAMES = {
+    0: "DTB_OK", 1: "DTB_ERR_NULL", 2: "DTB_ERR_DTYPE", 3: "DTB_ERR_SHAPE", 4: "DTB_ERR_ALIGN",
+    5: "DTB_ERR_ARCH", 6: "DTB_ERR_WORKSPACE", 7: "DTB_ERR_LAUNCH", 8: "DTB_ERR_TIMEOUT",
+    9: "DTB_ERR_UNSUPPORTED",
+}
+
+FLAG_ZERO_PADDED_ROWS = 0x1
+FLAG_BOUNDED_LOGITS = 0x2
+
+# Every symbol the public header declares; tests check that the library exports all of them.
+EXPORTED_SYMBOLS = (
+    "dtb_version", "dtb_status_string", "dtb_attn_supported", "dtb_attn_workspace_bytes",
+    "dtb_attn_fwd", "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands",
+    "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv",
+)
+
+
+class AttnParams(ctypes.Structure):
+    """Mirror of ``dtb_attn_params``."""
+
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("o", ctypes.c_void_p),
+        ("B", ctypes.c_int32), ("Hq", ctypes.c_int32), ("Hkv", ctypes.c_int32),
+        ("Sq", ctypes.c_int32), ("Skv", ctypes.c_int32), ("D", ctypes.c_int32),
+        ("q_stride_b", ctypes.c_int64), ("q_stride_h", ctypes.c_int64), ("q_stride_s", ctypes.c_int64),
+        ("k_stride_b", ctypes.c_int64), ("k_stride_h", ctypes.c_int64), ("k_stride_s", ctypes.c_int64),
+        ("v_stride_b", ctypes.c_int64), ("v_stride_h", ctypes.c_int64), ("v_stride_s", ctypes.c_int64),
+        ("o_stride_b", ctypes.c_int64), ("o_stride_h", ctypes.c_int64), ("o_stride_s", ctypes.c_int64),
+        ("kv_len", ctypes.c_void_p), ("mk", ctypes.c_void_p),
+        ("scale", ctypes.c_float), ("flags", ctypes.c_uint32), ("num_splits", ctypes.c_int32),
+        ("status", ctypes.c_void_p),
+    ]
+
+
+class AttnResidual(ctypes.Structure):
+    """Mirror of ``dtb_attn_residual``."""
+
+    _fields_ = [
+        ("o_acc", ctypes.c_void_p), ("m", ctypes.c_void_p), ("l", ctypes.c_void_p),
+        ("kv_offset", ctypes.c_int32), ("q_offset", ctypes.c_int32), ("init", ctypes.c_int32),
+    ]
+
+
+_lock = threading.Lock()
+_lib = None
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def load(build_if_missing: bool = True) -> ctypes.CDLL:
+    """Loads (building first if the binary is absent) and returns the shared library."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = _build.LIB_PATH
+        if not os.path.exists(path):
+            if not build_if_missing:
+                raise RuntimeError(f"{path} is missing; run `python -m dtb200.build`")
+            _build.build()
+        lib = ctypes.CDLL(path)
+        vp, i32p = ctypes.c_void_p, ctypes.c_void_p
+        lib.dtb_version.restype = ctypes.c_int
+        lib.dtb_status_string.restype = ctypes.c_char_p
+        lib.dtb_status_string.argtypes = [ctypes.c_int]
+        lib.dtb_attn_supported.restype = ctypes.c_int
+        lib.dtb_attn_supported.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(ctypes.c_int)]
+        lib.dtb_attn_workspace_bytes.restype = ctypes.c_size_t
+        lib.dtb_attn_workspace_bytes.argtypes = [ctypes.POINTER(AttnParams)]
+        lib.dtb_attn_fwd.restype = ctypes.c_int
+        lib.dtb_attn_fwd.argtypes = [ctypes.POINTER(AttnParams), vp, ctypes.c_size_t, vp]
+        lib.dtb_attn_fwd_residual.restype = ctypes.c_int
+        lib.dtb_attn_fwd_residual.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnResidual), vp]
+        lib.dtb_attn_finalize.restype = ctypes.c_int
+        lib.dtb_attn_finalize.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnResidual), vp]
+        lib.dtb_fixed_m_operands.restype = ctypes.c_int
+        lib.dtb_fixed_m_operands.argtypes = [ctypes.POINTER(AttnParams), ctypes.c_float, vp, vp, vp]
+        for name in ("dtb_selftest_tmem_roundtrip",):
+            fn = getattr(lib, name)
+            fn.restype = ctypes.c_int
+            fn.argtypes = [vp, vp, i32p, vp]
+        for name in ("dtb_selftest_qk", "dtb_selftest_pv"):
+            fn = getattr(lib, name)
+            fn.restype = ctypes.c_int
+            fn.argtypes = [vp, vp, vp, i32p, vp]
+        _lib = lib
+        return lib
+
+
+def status_string(code: int) -> str:
+    return load().dtb_status_string(int(code)).decode()
+
+
+def check(code: int, what: str) -> None:
+    """Maps a C-ABI status to the exception the reference's Python API would raise."""
+    if code == DTB_OK:
+        return
+    msg = f"{what}: {STATUS_NAMES.get(code, code)} ({status_string(code)})"
+    if code in (2, 3, 9):
+        raise NotImplementedError(msg)
+    if code in (1, 4, 6):
+        raise ValueError(msg)
+    raise RuntimeError(msg)

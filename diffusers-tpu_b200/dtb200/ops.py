@@ -1,0 +1,323 @@
+"""Device-local joint attention: the host-side mirror of the reference's kernel entry points.
+
+``attention`` and ``residual_attention`` keep the keyword surface of
+``diffusers_tpu/kernels/splash.py:566-650`` and ``:665-742`` (``query, key, value`` laid out
+``[B, heads, seq, dim]``, ``scale=None`` meaning ``1/sqrt(dim)``, output in ``query``'s dtype);
+``sdpa`` keeps the SDPA signature of ``diffusers_tpu/kernels/mesh_attention.py:218-228``
+(the mask / dropout / causal / gqa arguments are accepted and ignored, as there).
+Tile-size keywords of the reference are accepted and ignored: tiling is fixed by the kernel.
+
+All compute goes through the C ABI in ``libdtb200_attn.so``; nothing here falls back to PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple, Union
+
+import torch
+
+from . import _lib
+
+LOG2_E = 1.44269504
+FIXED_M_SAFE_BOUND = 213.0        # diffusers_tpu/kernels/fixed_m_bound.py:44-47
+FIXED_M_RING_SAFE_BOUND = 106.5   # diffusers_tpu/kernels/fixed_m_bound.py:49-54
+
+KvLen = Union[None, int, torch.Tensor]
+
+_status_bufs: dict = {}
+_workspaces: dict = {}
+
+
+def _status_buffer(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    buf = _status_bufs.get(key)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=device)
+        _status_bufs[key] = buf
+    return buf
+
+
+def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
+    if nbytes == 0:
+        return None
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def check_device_status(device: Union[torch.device, str, None] = None) -> None:
+    """Synchronises ``device`` and raises if a kernel reported a bounded wait that ran out."""
+    device = torch.device(device if device is not None else "cuda")
+    torch.cuda.synchronize(device)
+    buf = _status_buffer(device)
+    st = buf.tolist()
+    if st[0] != 0:
+        buf.zero_()
+        raise RuntimeError(
+            f"dtb200 kernel error {st[0]} (1 = wait timeout) at site {st[1]}, CTA {st[2]}, detail {st[3]}"
+        )
+
+
+def _check_inputs(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor) -> None:
+    for name, t in (("query", query), ("key", key), ("value", value)):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor: dtb200 has no CPU path")
+        if t.dtype != torch.bfloat16:
+            raise NotImplementedError(f"{name} must be bfloat16, got {t.dtype}")
+        if t.dim() != 4:
+            raise ValueError(f"{name} must be [B, heads, seq, dim], got shape {tuple(t.shape)}")
+    if query.shape[-1] != 128 or key.shape[-1] != 128 or value.shape[-1] != 128:
+        raise NotImplementedError("head_dim must be 128")
+    if key.shape != value.shape:
+        raise ValueError("key and value must have the same shape")
+    if query.shape[0] != key.shape[0]:
+        raise ValueError("batch sizes differ")
+    if query.shape[1] % key.shape[1] != 0:
+        raise ValueError("query heads must be a multiple of key/value heads")
+
+
+def _dense_last(t: torch.Tensor) -> torch.Tensor:
+    """Returns ``t`` if the kernel can address it in place (contiguous head_dim, 16-byte strides)."""
+    ok = t.stride(-1) == 1 and all((s * 2) % 16 == 0 for s in t.stride()[:-1]) and t.data_ptr() % 16 == 0
+    return t if ok else t.contiguous()
+
+
+def _kv_len_tensor(kv_len: KvLen, batch: int, device: torch.device) -> Optional[torch.Tensor]:
+    if kv_len is None:
+        return None
+    if isinstance(kv_len, torch.Tensor):
+        t = kv_len.to(device=device, dtype=torch.int32).reshape(-1)
+        if t.numel() == 1 and batch > 1:
+            t = t.expand(batch)
+        if t.numel() != batch:
+            raise ValueError(f"kv_len must have 1 or {batch} entries, got {t.numel()}")
+        return t.contiguous()
+    return torch.full((batch,), int(kv_len), dtype=torch.int32, device=device)
+
+
+def _fill_params(query, key, value, out, kv_len_t, mk, scale, flags, num_splits, status) -> _lib.AttnParams:
+    p = _lib.AttnParams()
+    p.q, p.k, p.v = query.data_ptr(), key.data_ptr(), value.data_ptr()
+    p.o = out.data_ptr() if out is not None else None
+    p.B, p.Hq, p.Sq, p.D = query.shape[0], query.shape[1], query.shape[2], query.shape[3]
+    p.Hkv, p.Skv = key.shape[1], key.shape[2]
+    p.q_stride_b, p.q_stride_h, p.q_stride_s = query.stride()[:3]
+    p.k_stride_b, p.k_stride_h, p.k_stride_s = key.stride()[:3]
+    p.v_stride_b, p.v_stride_h, p.v_stride_s = value.stride()[:3]
+    if out is not None:
+        p.o_stride_b, p.o_stride_h, p.o_stride_s = out.stride()[:3]
+    p.kv_len = kv_len_t.data_ptr() if kv_len_t is not None else None
+    p.mk = mk.data_ptr() if mk is not None else None
+    p.scale = float(scale) if scale is not None else 0.0
+    p.flags = flags
+    p.num_splits = int(num_splits)
+    p.status = status.data_ptr() if status is not None else None
+    return p
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def fixed_m_operands(query: torch.Tensor, key: torch.Tensor, *, scale: Optional[float] = None,
+                     gate: float = FIXED_M_SAFE_BOUND) -> torch.Tensor:
+    """``(2, heads)`` f32 bounded-logit operand: row 0 = ceil(Cauchy-Schwarz bound), row 1 = eligibility.
+
+    Mirrors ``fixed_m_bound.fixed_m_operands`` over ``fixed_m_query_norms``
+    (``diffusers_tpu/kernels/fixed_m_bound.py:76-118``): the bound is the product of the largest
+    scaled query row norm and the largest key row norm of each head, over batch and sequence.
+    """
+    _check_inputs(query, key, key)
+    query, key = _dense_last(query), _dense_last(key)
+    dev = query.device
+    norms = torch.empty(query.shape[1] + key.shape[1], dtype=torch.float32, device=dev)
+    mk = torch.empty(2, query.shape[1], dtype=torch.float32, device=dev)
+    p = _fill_params(query, key, key, None, None, None, scale, 0, 1, None)
+    with torch.cuda.device(dev):
+        st = _lib.load().dtb_fixed_m_operands(ctypes.byref(p), float(gate), norms.data_ptr(), mk.data_ptr(),
+                                              _stream_ptr(dev))
+    _lib.check(st, "dtb_fixed_m_operands")
+    return mk
+
+
+def attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    *,
+    scale: Optional[float] = None,
+    block_q: Optional[int] = None,
+    block_kv: Optional[int] = None,
+    block_kv_compute: Optional[int] = None,
+    use_fixed_m: bool = False,
+    qk_fp8: bool = False,
+    kv_len: KvLen = None,
+    kv_mask_all: bool = False,
+    unroll: Optional[bool] = None,
+    mk: Optional[torch.Tensor] = None,
+    zero_padded_rows: bool = True,
+    num_splits: int = 0,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Normalised joint attention, ``(B, heads, seq_q, dim)`` in ``query``'s dtype.
+
+    Same contract as ``diffusers_tpu/kernels/splash.py:566-650``.  ``kv_len`` may be an int, a
+    0-d tensor (the reference's traced scalar) or a ``[B]`` tensor, which replaces the
+    reference's per-sample Python loop (``diffusers_tpu/models/moss_image/jax_dit.py:199-203``).
+    Keys at or past ``kv_len`` are masked; with ``zero_padded_rows`` query rows at or past it
+    come back as exact zeros, so padding content cannot reach real rows or leak downstream.
+    ``use_fixed_m`` selects the per-head constant-offset softmax for heads whose bound passes the
+    gate (``mk`` supplies a precomputed operand, otherwise it is derived from this call's q and k).
+    ``block_*``, ``kv_mask_all`` and ``unroll`` are accepted for signature parity and ignored.
+    """
+    del block_q, block_kv, block_kv_compute, kv_mask_all, unroll
+    if qk_fp8:
+        raise NotImplementedError("qk_fp8 (E4M3 Q/K) is not built yet")
+    _check_inputs(query, key, value)
+    query, key, value = _dense_last(query), _dense_last(key), _dense_last(value)
+    dev = query.device
+    if out is None:
+        out = torch.empty(query.shape, dtype=query.dtype, device=dev)
+    kv_len_t = _kv_len_tensor(kv_len, query.shape[0], dev)
+    flags = 0
+    if zero_padded_rows and kv_len_t is not None:
+        flags |= _lib.FLAG_ZERO_PADDED_ROWS
+    if use_fixed_m:
+        if mk is None:
+            mk = fixed_m_operands(query, key, scale=scale)
+        flags |= _lib.FLAG_BOUNDED_LOGITS
+    else:
+        mk = None
+    status = _status_buffer(dev)
+    p = _fill_params(query, key, value, out, kv_len_t, mk, scale, flags, num_splits, status)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, lib.dtb_attn_workspace_bytes(ctypes.byref(p)))
+        st = lib.dtb_attn_fwd(ctypes.byref(p), ws.data_ptr() if ws is not None else None,
+                              ws.numel() if ws is not None else 0, _stream_ptr(dev))
+    _lib.check(st, "dtb_attn_fwd")
+    return out
+
+
+class ResidualState:
+    """Running ``(o, m, l)`` of a ring: ``o`` f32 ``[B,H,Sq,D]`` unnormalised, ``m``/``l`` f32 ``[B,H,Sq]``.
+
+    ``m`` is in log2 units of the scaled logits, so ``lse = m + log2(l)`` is the m-invariant
+    quantity the reference's ring merges on (``diffusers_tpu/kernels/splash.py:657-662``).
+    """
+
+    def __init__(self, batch: int, heads: int, seq_q: int, device: torch.device):
+        self.o = torch.empty(batch, heads, seq_q, 128, dtype=torch.float32, device=device)
+        self.m = torch.empty(batch, heads, seq_q, dtype=torch.float32, device=device)
+        self.l = torch.empty(batch, heads, seq_q, dtype=torch.float32, device=device)
+        self.fresh = True
+
+
+def residual_attention_(
+    state: ResidualState,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    *,
+    scale: Optional[float] = None,
+    use_fixed_m: bool = False,
+    mk: Optional[torch.Tensor] = None,
+    kv_len: KvLen = None,
+    kv_offset: int = 0,
+    q_offset: int = 0,
+) -> ResidualState:
+    """Folds one KV shard into ``state`` in place (the fused kernel + merge step of a ring)."""
+    _check_inputs(query, key, value)
+    if use_fixed_m and mk is None:
+        raise ValueError("use_fixed_m needs the (2, heads) operand mk.")
+    query, key, value = _dense_last(query), _dense_last(key), _dense_last(value)
+    dev = query.device
+    kv_len_t = _kv_len_tensor(kv_len, query.shape[0], dev)
+    flags = _lib.FLAG_BOUNDED_LOGITS if use_fixed_m else 0
+    p = _fill_params(query, key, value, None, kv_len_t, mk if use_fixed_m else None, scale, flags, 1,
+                     _status_buffer(dev))
+    r = _lib.AttnResidual(state.o.data_ptr(), state.m.data_ptr(), state.l.data_ptr(), int(kv_offset),
+                          int(q_offset), 1 if state.fresh else 0)
+    with torch.cuda.device(dev):
+        st = _lib.load().dtb_attn_fwd_residual(ctypes.byref(p), ctypes.byref(r), _stream_ptr(dev))
+    _lib.check(st, "dtb_attn_fwd_residual")
+    state.fresh = False
+    return state
+
+
+def finalize_residual(state: ResidualState, *, dtype: torch.dtype = torch.bfloat16, kv_len: KvLen = None,
+                      q_offset: int = 0, zero_padded_rows: bool = True,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``o / l`` cast to bf16: the epilogue of ``splash.py:367-375`` applied to a merged ring state."""
+    if dtype != torch.bfloat16:
+        raise NotImplementedError("only bfloat16 outputs are supported")
+    dev = state.o.device
+    B, H, Sq, D = state.o.shape
+    if out is None:
+        out = torch.empty(B, H, Sq, D, dtype=torch.bfloat16, device=dev)
+    kv_len_t = _kv_len_tensor(kv_len, B, dev)
+    flags = _lib.FLAG_ZERO_PADDED_ROWS if (zero_padded_rows and kv_len_t is not None) else 0
+    p = _lib.AttnParams()
+    p.o = out.data_ptr()
+    p.B, p.Hq, p.Hkv, p.Sq, p.Skv, p.D = B, H, H, Sq, Sq, D
+    p.o_stride_b, p.o_stride_h, p.o_stride_s = out.stride()[:3]
+    p.kv_len = kv_len_t.data_ptr() if kv_len_t is not None else None
+    p.flags = flags
+    r = _lib.AttnResidual(state.o.data_ptr(), state.m.data_ptr(), state.l.data_ptr(), 0, int(q_offset), 0)
+    with torch.cuda.device(dev):
+        st = _lib.load().dtb_attn_finalize(ctypes.byref(p), ctypes.byref(r), _stream_ptr(dev))
+    _lib.check(st, "dtb_attn_finalize")
+    return out
+
+
+def residual_attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    *,
+    scale: Optional[float] = None,
+    block_q: Optional[int] = None,
+    block_kv: Optional[int] = None,
+    block_kv_compute: Optional[int] = None,
+    use_fixed_m: bool = False,
+    qk_fp8: bool = False,
+    mk: Optional[torch.Tensor] = None,
+    kv_len: KvLen = None,
+    kv_offset: int = 0,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """One KV shard's unnormalised ``(o, m, l)``: ``o`` f32 ``[B,H,Sq,D]``, ``m``/``l`` f32 ``[B,H,Sq,1]``.
+
+    Same contract as ``diffusers_tpu/kernels/splash.py:665-742`` (raises ``ValueError`` when
+    ``use_fixed_m`` is set without ``mk``, as the reference does at ``:712-713``).
+    """
+    del block_q, block_kv, block_kv_compute
+    if qk_fp8:
+        raise NotImplementedError("qk_fp8 (E4M3 Q/K) is not built yet")
+    if use_fixed_m and mk is None:
+        raise ValueError("use_fixed_m needs the (2, heads) operand mk.")
+    _check_inputs(query, key, value)
+    state = ResidualState(query.shape[0], query.shape[1], query.shape[2], query.device)
+    residual_attention_(state, query, key, value, scale=scale, use_fixed_m=use_fixed_m, mk=mk, kv_len=kv_len,
+                        kv_offset=kv_offset)
+    return state.o, state.m.unsqueeze(-1), state.l.unsqueeze(-1)
+
+
+def sdpa(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    attn_mask: Optional[torch.Tensor] = None,
+    dropout_p: float = 0.0,
+    is_causal: bool = False,
+    scale: Optional[float] = None,
+    enable_gqa: bool = False,
+    *,
+    kv_len: KvLen = None,
+    use_fixed_m: bool = False,
+) -> torch.Tensor:
+    """SDPA-signature callable, ``[B, H, S, D]`` in and out (``mesh_attention.py:218-228``)."""
+    del attn_mask, dropout_p, is_causal, enable_gqa  # Not supported, as in the reference.
+    return attention(query, key, value, scale=scale, kv_len=kv_len, use_fixed_m=use_fixed_m)

@@ -1,0 +1,114 @@
+/* dtb200_attn.h — C ABI of the B200 joint (text + image/video token) attention forward.
+ *
+ * Every entry point is a plain `extern "C"` function taking raw device pointers and sizes, so it can
+ * be bound from a torch custom op (ctypes / cpp extension), from a `jax.ffi` custom call handler or
+ * from any other host language.  No entry point allocates or frees device memory except where stated,
+ * none synchronises the stream, and all work is enqueued on the `stream` argument.
+ *
+ * Tensors are bf16 laid out [B, H, S, D] with arbitrary element strides for B, H and S and a
+ * contiguous last dimension (D == 128).  Byte strides must be multiples of 16 and base pointers
+ * 16-byte aligned (TMA tensor-map rules).
+ *
+ * Each declaration cites the function of the reference project (shungcp/diffusers-tpu) that it
+ * replaces, by path within that project.
+ */
+#ifndef DTB200_ATTN_H_
+#define DTB200_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Host-side status codes returned by every entry point (0 = success). */
+enum dtb_status {
+  DTB_OK = 0,
+  DTB_ERR_NULL = 1,      /* a required pointer is NULL                                   */
+  DTB_ERR_DTYPE = 2,     /* unsupported element type                                     */
+  DTB_ERR_SHAPE = 3,     /* unsupported shape (head_dim != 128, H % Hkv != 0, sizes <= 0) */
+  DTB_ERR_ALIGN = 4,     /* pointer or stride breaks the 16-byte rule                    */
+  DTB_ERR_ARCH = 5,      /* the current device is not sm_100                             */
+  DTB_ERR_WORKSPACE = 6, /* workspace missing or too small                               */
+  DTB_ERR_LAUNCH = 7,    /* CUDA reported an error when encoding maps or launching       */
+  DTB_ERR_TIMEOUT = 8,   /* a bounded device wait ran out (reported via the status word) */
+  DTB_ERR_UNSUPPORTED = 9
+};
+
+/* Flags for dtb_attn_params.flags */
+#define DTB_FLAG_ZERO_PADDED_ROWS 0x1u /* write exact zeros to query rows >= kv_len[b]            */
+#define DTB_FLAG_BOUNDED_LOGITS 0x2u   /* per-head constant softmax offset from `mk` (fixed-m)    */
+#define DTB_FLAG_SIMPLE_KERNEL 0x4u    /* force the single-tile validation kernel                 */
+
+/* One attention call.  All pointers are device pointers unless noted. */
+typedef struct dtb_attn_params {
+  const void* q; /* bf16 [B, Hq,  Sq,  D] */
+  const void* k; /* bf16 [B, Hkv, Skv, D] */
+  const void* v; /* bf16 [B, Hkv, Skv, D] */
+  void* o;       /* bf16 [B, Hq,  Sq,  D] (ignored by the residual entry point) */
+  int32_t B, Hq, Hkv, Sq, Skv, D;
+  /* element strides of the batch, head and sequence axes (last axis is contiguous) */
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  int64_t k_stride_b, k_stride_h, k_stride_s;
+  int64_t v_stride_b, v_stride_h, v_stride_s;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  const int32_t* kv_len; /* [B] valid key count per batch element (keys >= kv_len are masked); NULL = all */
+  const float* mk;       /* [2, Hq] bounded-logit operand: row 0 = integral bound m, row 1 = eligibility; NULL = online softmax */
+  float scale;           /* softmax scale; <= 0 means 1/sqrt(D) */
+  uint32_t flags;        /* DTB_FLAG_* */
+  int32_t num_splits;    /* split-KV factor: 0 = choose automatically, 1 = none, n > 1 = force (needs workspace) */
+  int32_t* status;       /* optional [4] int32 device status words written when a bounded wait runs out; must be zeroed by the caller */
+} dtb_attn_params;
+
+/* Running state of a residual (ring) accumulation, in the reference's units: `m` and `lse` are in
+ * log2 units of the scaled logits.  o_acc f32 [B, Hq, Sq, D] contiguous; m, l f32 [B, Hq, Sq]. */
+typedef struct dtb_attn_residual {
+  float* o_acc;
+  float* m;
+  float* l;
+  int32_t kv_offset; /* global index of this shard's first key (kv_len is compared against global indices) */
+  int32_t q_offset;  /* global index of the first query row of this call (used to zero padded rows) */
+  int32_t init;      /* non-zero: start from the empty state instead of reading o_acc / m / l */
+} dtb_attn_residual;
+
+/* Library version and a human-readable string for a status code. */
+int dtb_version(void);
+const char* dtb_status_string(int status);
+
+/* 1 when the call described by `p` is supported on the current device, else 0 and *why (if not NULL)
+ * receives the status that dtb_attn_fwd would return. */
+int dtb_attn_supported(const dtb_attn_params* p, int* why);
+
+/* Scratch bytes needed by dtb_attn_fwd for `p` (0 unless split-KV is in effect). */
+size_t dtb_attn_workspace_bytes(const dtb_attn_params* p);
+
+/* Normalised joint attention forward: o = softmax(scale * q k^T + key_mask) v.
+ * Replaces diffusers_tpu/kernels/splash.py:566-650 `attention(...)` (and the per-sample loop around it
+ * in diffusers_tpu/models/moss_image/jax_dit.py:199-203: kv_len is per batch element here). */
+int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Residual forward over one KV shard: folds this shard into the running (o_acc, m, l) state.
+ * Replaces diffusers_tpu/kernels/splash.py:665-742 `residual_attention(...)` together with the
+ * LSE-space merge its docstring prescribes (splash.py:657-662, 688-691). */
+int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_residual* r, void* stream);
+
+/* Normalises a finished running state: o = o_acc / l, cast to bf16 (rows with l == 0 give zeros).
+ * Replaces the epilogue of diffusers_tpu/kernels/splash.py:367-375 applied after a ring. */
+int dtb_attn_finalize(const dtb_attn_params* p, const dtb_attn_residual* r, void* stream);
+
+/* Bounded-logit operand: mk[0,h] = ceil(max_row|q*scale*log2e| * max_row|k|), mk[1,h] = (bound <= gate).
+ * `norms` is a scratch of Hq + Hkv floats (device).  Replaces
+ * diffusers_tpu/kernels/fixed_m_bound.py:57-118 `max_row_norm_per_head` + `fixed_m_operands`. */
+int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float* norms, float* mk_out, void* stream);
+
+/* Hardware self-tests of the descriptor encodings the kernels rely on (one 128x128x128 tile each).
+ * They write f32 [128,128] results for the host to compare; no reference counterpart. */
+int dtb_selftest_tmem_roundtrip(const float* in, float* out, int32_t* status, void* stream);
+int dtb_selftest_qk(const void* q, const void* k, float* s_out, int32_t* status, void* stream);
+int dtb_selftest_pv(const void* p, const void* v, float* o_out, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DTB200_ATTN_H_ */
