@@ -212,7 +212,7 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
   int st = check_params(p, true);
   if (st != DTB_OK) return st;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
-  if (ensure_kernel_attrs() != cudaSuccess) return DTB_ERR_LAUNCH;
+  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
   AttnKernelParams kp;
   st = fill_kernel_params(p, &kp);
   if (st != DTB_OK) return st;
@@ -230,7 +230,7 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
   if (splits == 1) {
     const dim3 grid(q_blocks(p), p->Hq, p->B);
     attn_fwd_kernel<false><<<grid, block, kSmemBytes, s>>>(kp);
-    return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+    return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
   }
   const size_t rows = static_cast<size_t>(splits) * p->B * p->Hq * p->Sq;
   kp.acc_o = static_cast<float*>(workspace);
@@ -240,12 +240,12 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
   kp.acc_init = 1;
   const dim3 grid(q_blocks(p), p->Hq, p->B * splits);
   attn_fwd_kernel<true><<<grid, block, kSmemBytes, s>>>(kp);
-  if (cudaGetLastError() != cudaSuccess) return DTB_ERR_LAUNCH;
+  if (!launch_ok("attn_fwd_kernel launch")) return DTB_ERR_LAUNCH;
   const int64_t out_rows = static_cast<int64_t>(p->B) * p->Hq * p->Sq;
   combine_kernel<<<static_cast<unsigned>((out_rows + 7) / 8), 256, 0, s>>>(
       kp.acc_o, kp.acc_m, kp.acc_l, splits, p->B, p->Hq, p->Sq, kp.o, kp.o_stride_b, kp.o_stride_h, kp.o_stride_s,
       p->kv_len, 0, kp.zero_padded_rows);
-  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+  return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
 
 extern "C" int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_residual* r, void* stream) {
@@ -254,7 +254,7 @@ extern "C" int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_re
   if (r == nullptr || r->o_acc == nullptr || r->m == nullptr || r->l == nullptr) return DTB_ERR_NULL;
   if (reinterpret_cast<uintptr_t>(r->o_acc) & 15u) return DTB_ERR_ALIGN;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
-  if (ensure_kernel_attrs() != cudaSuccess) return DTB_ERR_LAUNCH;
+  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
   AttnKernelParams kp;
   st = fill_kernel_params(p, &kp);
   if (st != DTB_OK) return st;
@@ -267,7 +267,7 @@ extern "C" int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_re
   kp.zero_padded_rows = 0;  // padded rows are zeroed by dtb_attn_finalize
   const dim3 grid(q_blocks(p), p->Hq, p->B);
   attn_fwd_kernel<true><<<grid, dim3(kNumThreads), kSmemBytes, static_cast<cudaStream_t>(stream)>>>(kp);
-  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+  return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
 
 extern "C" int dtb_attn_finalize(const dtb_attn_params* p, const dtb_attn_residual* r, void* stream) {
@@ -280,7 +280,7 @@ extern "C" int dtb_attn_finalize(const dtb_attn_params* p, const dtb_attn_residu
   combine_kernel<<<static_cast<unsigned>((out_rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       r->o_acc, r->m, r->l, 1, p->B, p->Hq, p->Sq, static_cast<__nv_bfloat16*>(p->o), p->o_stride_b, p->o_stride_h,
       p->o_stride_s, p->kv_len, r->q_offset, (p->flags & DTB_FLAG_ZERO_PADDED_ROWS) ? 1 : 0);
-  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+  return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
 
 extern "C" int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float* norms, float* mk_out, void* stream) {
@@ -289,7 +289,7 @@ extern "C" int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float*
   if (norms == nullptr || mk_out == nullptr) return DTB_ERR_NULL;
   if ((reinterpret_cast<uintptr_t>(p->q) & 7u) || (reinterpret_cast<uintptr_t>(p->k) & 7u)) return DTB_ERR_ALIGN;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (cudaMemsetAsync(norms, 0, sizeof(float) * (p->Hq + p->Hkv), s) != cudaSuccess) return DTB_ERR_LAUNCH;
+  if (!cuda_ok(cudaMemsetAsync(norms, 0, sizeof(float) * (p->Hq + p->Hkv), s), "cudaMemsetAsync")) return DTB_ERR_LAUNCH;
   const float scale = p->scale > 0.f ? p->scale : 1.0f / sqrtf(static_cast<float>(p->D));
   // The reference takes the norm of the bf16-rounded product q * scale * log2(e); this kernel
   // applies the scale in f32 after the MMA, so the norm of the unrounded product is the exact bound.
@@ -301,5 +301,5 @@ extern "C" int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float*
       static_cast<const __nv_bfloat16*>(p->k), p->B, p->Hkv, p->Skv, p->k_stride_b, p->k_stride_h, p->k_stride_s, 1.0f,
       norms + p->Hq);
   fixed_m_finish_kernel<<<(p->Hq + 127) / 128, 128, 0, s>>>(norms, p->Hq, p->Hkv, gate, mk_out);
-  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+  return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }

@@ -1,11 +1,14 @@
 // Joint-attention forward for sm_100a: one CTA owns 256 query rows (two 128-row
 // tiles) of one (batch, head) and sweeps the valid keys in 128-key tiles.
 //
-// Warp roles (320 threads):
+// Warp roles (384 threads = 3 warpgroups):
 //   warps 0-3   softmax group 0: one thread per query row of tile 0
 //   warps 4-7   softmax group 1: one thread per query row of tile 1
 //   warp  8     MMA issuer (lane 0 issues tcgen05.mma; the warp stays converged)
 //   warp  9     TMA producer (lane 0 issues the tensor loads)
+//   warps 10-11 idle; they exist so that warps 8-11 form a whole warpgroup, which is the
+//               unit setmaxnreg works on: that warpgroup hands registers to the softmax groups
+//               (each SM sub-partition holds 16384 registers shared by one warp of each group).
 //
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 f32 columns each.  P (bf16)
 // is written over the first 64 columns of its S tile and consumed from tensor
@@ -38,7 +41,9 @@ constexpr uint32_t kTileBytes = 2 * kPanelBytes;
 constexpr int kNumSoftmaxThreads = kQTiles * kBlockM;
 constexpr int kMmaWarp = kNumSoftmaxThreads / 32;
 constexpr int kLoadWarp = kMmaWarp + 1;
-constexpr int kNumThreads = kNumSoftmaxThreads + 64;
+constexpr int kNumThreads = kNumSoftmaxThreads + 128;
+constexpr int kRegsSoftmax = 224;              // 2 * 32 * 224 + 32 * 56 = 16128 <= 16384 per sub-partition
+constexpr int kRegsService = 56;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units: rescale O only when the row max grew by > 2^8
 constexpr float kFixedMRecenter = 88.0f;     // bounded-logit mode exponent offset (m - 88)
@@ -164,7 +169,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
 //                                 (ring steps and split-KV partials).
 // ---------------------------------------------------------------------------
 template <bool kResidual>
-__global__ void __maxnreg__(200) attn_fwd_kernel(const __grid_constant__ AttnKernelParams p) {
+__global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnKernelParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem;
   {
@@ -248,6 +253,7 @@ __global__ void __maxnreg__(200) attn_fwd_kernel(const __grid_constant__ AttnKer
 
   if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA producer
+    setmaxnreg_dec<kRegsService>();
     bool ok = true;
     if (lane == 0) {
       for (int t = 0; t < kQTiles; ++t) {
@@ -274,6 +280,7 @@ __global__ void __maxnreg__(200) attn_fwd_kernel(const __grid_constant__ AttnKer
     __syncwarp();
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
+    setmaxnreg_dec<kRegsService>();
     constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBlockN, false, false);
     constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, kHeadDim, false, true);
     const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(smem_q), 16, 1024);
@@ -353,8 +360,9 @@ __global__ void __maxnreg__(200) attn_fwd_kernel(const __grid_constant__ AttnKer
         }
       }
     }
-  } else {
+  } else if (warp < kMmaWarp) {
     // ------------------------------------------------------------------ softmax groups
+    setmaxnreg_inc<kRegsSoftmax>();
     const int t = warp >> 2;                       // query tile of this group
     const int row_in_tile = threadIdx.x & (kBlockM - 1);
     const int row = q0 + t * kBlockM + row_in_tile;  // query row within this call
@@ -479,6 +487,10 @@ __global__ void __maxnreg__(200) attn_fwd_kernel(const __grid_constant__ AttnKer
         }
       }
     }
+  }
+
+  else {
+    setmaxnreg_dec<kRegsService>();  // idle warps of the service warpgroup
   }
 
   // ------------------------------------------------------------------ teardown

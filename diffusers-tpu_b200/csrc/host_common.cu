@@ -1,8 +1,24 @@
 #include "host_common.h"
 
+#include <cstdio>
 #include <mutex>
 
 namespace dtb {
+
+namespace {
+thread_local char g_detail[256] = "";
+}
+
+bool cuda_ok(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return true;
+  snprintf(g_detail, sizeof(g_detail), "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+  (void)cudaGetLastError();
+  return false;
+}
+
+bool launch_ok(const char* what) { return cuda_ok(cudaGetLastError(), what); }
+
+const char* last_detail() { return g_detail; }
 
 EncodeTiledFn get_encode_tiled() {
   static EncodeTiledFn fn = nullptr;
@@ -20,7 +36,10 @@ EncodeTiledFn get_encode_tiled() {
 int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb,
                    int64_t sh, int64_t ss, int box_rows) {
   EncodeTiledFn enc = get_encode_tiled();
-  if (enc == nullptr) return DTB_ERR_LAUNCH;
+  if (enc == nullptr) {
+    snprintf(g_detail, sizeof(g_detail), "cuTensorMapEncodeTiled entry point not found");
+    return DTB_ERR_LAUNCH;
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return DTB_ERR_ALIGN;
   const int64_t esz = 2;
   if (((ss * esz) & 15) || ((sh * esz) & 15) || ((sb * esz) & 15)) return DTB_ERR_ALIGN;
@@ -39,7 +58,12 @@ int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstr, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? DTB_OK : DTB_ERR_LAUNCH;
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_detail, sizeof(g_detail), "cuTensorMapEncodeTiled failed with CUresult %d (S=%lld H=%lld B=%lld)",
+             static_cast<int>(r), static_cast<long long>(S), static_cast<long long>(H), static_cast<long long>(B));
+    return DTB_ERR_LAUNCH;
+  }
+  return DTB_OK;
 }
 
 bool device_is_sm100() {
@@ -53,6 +77,8 @@ bool device_is_sm100() {
 }  // namespace dtb
 
 extern "C" int dtb_version(void) { return 100; }
+
+extern "C" const char* dtb_last_error_detail(void) { return dtb::last_detail(); }
 
 extern "C" const char* dtb_status_string(int status) {
   switch (status) {

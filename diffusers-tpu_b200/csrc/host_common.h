@@ -25,6 +25,13 @@ EncodeTiledFn get_encode_tiled();
 int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb,
                    int64_t sh, int64_t ss, int box_rows);
 
+// Records the CUDA error behind a DTB_ERR_LAUNCH so that dtb_last_error_detail() can name it.
+// Returns true when `e` is cudaSuccess.
+bool cuda_ok(cudaError_t e, const char* what);
+// Checks (and clears) the launch error of the kernel just enqueued.
+bool launch_ok(const char* what);
+const char* last_detail();
+
 // True when the current device is compute capability 10.x.
 bool device_is_sm100();
 

@@ -179,14 +179,14 @@ int launch_tile_test(int mode, const void* a, const void* b, float* out, int32_t
   cudaError_t e;
   if (mode == 0) {
     e = cudaFuncSetAttribute(mma_tile_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return DTB_ERR_LAUNCH;
+    if (!cuda_ok(e, "cudaFuncSetAttribute")) return DTB_ERR_LAUNCH;
     mma_tile_kernel<0><<<1, 128, smem, s>>>(ta, tb, static_cast<const __nv_bfloat16*>(a), out, status);
   } else {
     e = cudaFuncSetAttribute(mma_tile_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return DTB_ERR_LAUNCH;
+    if (!cuda_ok(e, "cudaFuncSetAttribute")) return DTB_ERR_LAUNCH;
     mma_tile_kernel<1><<<1, 128, smem, s>>>(ta, tb, static_cast<const __nv_bfloat16*>(a), out, status);
   }
-  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+  return launch_ok("selftest launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
 
 }  // namespace
@@ -196,7 +196,7 @@ extern "C" int dtb_selftest_tmem_roundtrip(const float* in, float* out, int32_t*
   if (in == nullptr || out == nullptr) return DTB_ERR_NULL;
   if (!dtb::device_is_sm100()) return DTB_ERR_ARCH;
   dtb::tmem_roundtrip_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(in, out, status);
-  return cudaGetLastError() == cudaSuccess ? DTB_OK : DTB_ERR_LAUNCH;
+  return dtb::launch_ok("selftest launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
 
 extern "C" int dtb_selftest_qk(const void* q, const void* k, float* s_out, int32_t* status, void* stream) {

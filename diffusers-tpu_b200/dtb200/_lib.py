@@ -23,7 +23,7 @@ FLAG_BOUNDED_LOGITS = 0x2
 
 # Every symbol the public header declares; tests check that the library exports all of them.
 EXPORTED_SYMBOLS = (
-    "dtb_version", "dtb_status_string", "dtb_attn_supported", "dtb_attn_workspace_bytes",
+    "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
     "dtb_attn_fwd", "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands",
     "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv",
 )
@@ -79,6 +79,7 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         lib.dtb_version.restype = ctypes.c_int
         lib.dtb_status_string.restype = ctypes.c_char_p
         lib.dtb_status_string.argtypes = [ctypes.c_int]
+        lib.dtb_last_error_detail.restype = ctypes.c_char_p
         lib.dtb_attn_supported.restype = ctypes.c_int
         lib.dtb_attn_supported.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(ctypes.c_int)]
         lib.dtb_attn_workspace_bytes.restype = ctypes.c_size_t
@@ -112,6 +113,9 @@ def check(code: int, what: str) -> None:
     if code == DTB_OK:
         return
     msg = f"{what}: {STATUS_NAMES.get(code, code)} ({status_string(code)})"
+    detail = load().dtb_last_error_detail().decode()
+    if code == 7 and detail:
+        msg += f" [{detail}]"
     if code in (2, 3, 9):
         raise NotImplementedError(msg)
     if code in (1, 4, 6):

@@ -12,7 +12,7 @@ All compute goes through the C ABI in ``libdtb200_attn.so``; nothing here falls 
 from __future__ import annotations
 
 import ctypes
-from typing import Optional, Tuple, Union
+from typing import Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -22,7 +22,7 @@ LOG2_E = 1.44269504
 FIXED_M_SAFE_BOUND = 213.0        # diffusers_tpu/kernels/fixed_m_bound.py:44-47
 FIXED_M_RING_SAFE_BOUND = 106.5   # diffusers_tpu/kernels/fixed_m_bound.py:49-54
 
-KvLen = Union[None, int, torch.Tensor]
+KvLen = Union[None, int, Sequence[int], torch.Tensor]
 
 _status_bufs: dict = {}
 _workspaces: dict = {}
@@ -95,6 +95,8 @@ def _kv_len_tensor(kv_len: KvLen, batch: int, device: torch.device) -> Optional[
         if t.numel() != batch:
             raise ValueError(f"kv_len must have 1 or {batch} entries, got {t.numel()}")
         return t.contiguous()
+    if isinstance(kv_len, (list, tuple)):
+        return _kv_len_tensor(torch.tensor(list(kv_len), dtype=torch.int32), batch, device)
     return torch.full((batch,), int(kv_len), dtype=torch.int32, device=device)
 
 

@@ -75,6 +75,8 @@ typedef struct dtb_attn_residual {
 /* Library version and a human-readable string for a status code. */
 int dtb_version(void);
 const char* dtb_status_string(int status);
+/* Text naming the CUDA error behind the calling thread's most recent DTB_ERR_LAUNCH ("" if none). */
+const char* dtb_last_error_detail(void);
 
 /* 1 when the call described by `p` is supported on the current device, else 0 and *why (if not NULL)
  * receives the status that dtb_attn_fwd would return. */
