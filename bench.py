@@ -1,0 +1,395 @@
+#!/usr/bin/env python
+"""Benchmark of the joint-attention forward: attention TFLOP/s (4*B*H*Sq*Sk*D per call).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2_image1024|c3_image2048|c4_video480p|c5_video768p]
+                    [--mode auto|local|ulysses|ring] [--fixed-m]
+
+A step is one DiT forward's worth of attention: ``layers`` (60 for the image workloads) independent
+seeded layer calls, each on its own q/k/v/o buffers, so consecutive calls never find their inputs in
+L2.  ``value`` is timed with CUDA events with inputs resident in HBM; ``e2e`` times the same calls
+through the public API from pinned host buffers, with the host->device copies of q, k, v and the
+device->host copy of the output inside the timed region.
+
+Under ``torchrun`` (N > 1) the default placement is the reference's head-parallel one with CFG halves
+on chip halves: batch elements first, then heads, are dealt to ranks and every rank runs the local
+kernel on its resident shard (no collective on the data path).  ``--mode ulysses`` starts and ends
+sequence-sharded with an all-to-all either side; ``--mode ring`` rotates K/V shards between ranks.
+
+``--impl reference`` times the CPU restatement of the reference's own CPU attention (fp32 softmax)
+on the host cores for the same workload and metric, on a bounded sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "diffusers-tpu_b200"))
+
+import torch  # noqa: E402
+
+METRIC = "attention_tflops"
+UNIT = "TFLOP/s"
+LAYERS = {"c1_image512_cpu": 60, "c2_image1024": 60, "c3_image2048": 60, "c4_video480p": 4, "c5_video768p": 1}
+# DRAM bytes per launch of attn_fwd_kernel on the c2 workload (dram__bytes_read.sum + dram__bytes_write.sum),
+# from the ncu capture summarised in profiles/attn_fwd_kernel_c2_image1024.txt.  None until captured.
+NCU_TRAFFIC_BYTES_C2 = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        exe = shutil.which("nvidia-smi")
+        if exe is None:
+            return
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
+        self.proc = subprocess.Popen(
+            [exe, f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+            stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, max_clock, reasons, power = [], None, set(), []
+        with open(self.path) as f:
+            for line in f:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    clocks.append(float(parts[1]))
+                    max_clock = float(parts[2])
+                    power.append(float(parts[3]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        if not clocks:
+            return None
+        # keep the samples taken under load (upper half), the first ones may predate the first launch
+        busy = sorted(clocks)[len(clocks) // 2:]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max_clock, "reasons": sorted(reasons),
+                "samples": len(clocks), "power_w_max": max(power) if power else None}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def placement(batch: int, heads: int, world: int):
+    """CFG halves on chip halves, then heads: returns (batch_groups, head_groups)."""
+    bg = min(batch, world)
+    while world % bg:
+        bg -= 1
+    hg = world // bg
+    if heads % hg:
+        raise SystemExit(f"{heads} heads do not divide over {hg} ranks per batch group; use --mode ring")
+    return bg, hg
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm: the oracle's fp32-softmax attention on the host cores
+# --------------------------------------------------------------------------------------------
+def cpu_attention_sample(cfg, sample_heads: int, min_seconds: float, max_reps: int):
+    from dtb200.inputs import make_inputs
+    from oracle import attn_oracle
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    q, k, v, kv_len = make_inputs(cfg, 0, heads=sample_heads)
+    q, k, v, kv_len = q[:1], k[:1], v[:1], kv_len[:1]
+    flops = 4.0 * 1 * sample_heads * cfg.seq * cfg.seq * cfg.head_dim
+    attn_oracle.attention_fp32(q[:, :1], k[:, :1], v[:, :1], kv_len=kv_len)  # warm the thread pool
+    times = []
+    t_all = time.perf_counter()
+    while len(times) < max_reps and (time.perf_counter() - t_all < min_seconds or not times):
+        t0 = time.perf_counter()
+        attn_oracle.attention_fp32(q, k, v, kv_len=kv_len)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    return {"value": flops / best / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{sample_heads} of {cfg.heads} heads of batch element 0 of one {cfg.name} layer call, "
+                      f"fp32 softmax on CPU, best of {len(times)}"}, times
+
+
+def run_reference(args, cfg):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    sample_heads = min(cfg.heads, 8 if cfg.seq <= 8192 else 1)
+    step_times = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base, times = cpu_attention_sample(cfg, sample_heads, 0.0, 1)
+        if i >= args.warmup:
+            step_times.append(times[0])
+    flops = 4.0 * sample_heads * cfg.seq * cfg.seq * cfg.head_dim
+    total = sum(step_times)
+    value = flops * len(step_times) / total / 1e12
+    base["value"] = value
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / len(step_times), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg.name, "B": cfg.batch, "H": cfg.heads, "S": cfg.seq, "D": cfg.head_dim,
+                   "step": base["sample"]},
+        "cpu_baseline": base,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------------
+def run_ours(args, cfg):
+    import torch.distributed as dist
+
+    import dtb200
+    from dtb200.inputs import make_inputs
+
+    rank, world, local = dist_env()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    mode = args.mode
+    if mode == "auto":
+        mode = "local"
+    layers = args.layers or LAYERS[cfg.name]
+    if mode != "local":
+        from dtb200 import parallel
+    bg, hg = placement(cfg.batch, cfg.heads, world) if mode == "local" else (1, 1)
+    b_local = cfg.batch // bg
+    h_local = cfg.heads // hg
+    my_b = (rank // hg) * b_local
+    my_h = (rank % hg) * h_local
+
+    # Resident inputs: one buffer set per layer call.
+    sets = []
+    for i in range(layers):
+        if mode == "local":
+            q, k, v, kv_len = make_inputs(cfg, i, device="cuda", heads=cfg.heads)
+            q = q[my_b:my_b + b_local, my_h:my_h + h_local].contiguous()
+            k = k[my_b:my_b + b_local, my_h:my_h + h_local].contiguous()
+            v = v[my_b:my_b + b_local, my_h:my_h + h_local].contiguous()
+            kv_len = kv_len[my_b:my_b + b_local].contiguous()
+        else:
+            q, k, v, kv_len = parallel.make_sequence_shard(cfg, i, rank, world, dev)
+        sets.append((q, k, v, kv_len, torch.empty_like(q)))
+    torch.cuda.synchronize()
+
+    mk = None
+    launches_per_call = 1
+
+    def layer_call(s):
+        q, k, v, kv_len, o = s
+        if mode == "local":
+            dtb200.attention(q, k, v, kv_len=kv_len, use_fixed_m=args.fixed_m, mk=mk, out=o)
+        elif mode == "ulysses":
+            parallel.ulysses_attention(q, k, v, kv_len=kv_len, out=o)
+        else:
+            parallel.ring_attention(q, k, v, kv_len=kv_len, out=o)
+
+    if args.fixed_m:
+        launches_per_call = 4  # two row-norm reductions, the operand kernel, the attention kernel
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        for s in sets:
+            layer_call(s)
+    barrier()
+    dtb200.check_device_status(dev)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        for s in sets:
+            layer_call(s)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    dtb200.check_device_status(dev)
+
+    # ---- end to end: pinned host buffers -> device -> kernel -> pinned host result, double buffered
+    n_host = min(layers, 4)
+    host_sets = []
+    for i in range(n_host):
+        q, k, v, kv_len, o = sets[i]
+        host_sets.append((q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory(), kv_len,
+                          torch.empty(o.shape, dtype=o.dtype).pin_memory()))
+    copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    compute = torch.cuda.current_stream(dev)
+    dev_bufs = [tuple(torch.empty_like(t) for t in sets[0][:3]) + (torch.empty_like(sets[0][4]),) for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    out_ready = [torch.cuda.Event() for _ in range(2)]
+    buf_free = [torch.cuda.Event() for _ in range(2)]
+    h2d_bytes = sum(t.numel() * t.element_size() for t in host_sets[0][:3]) * layers * world
+    d2h_bytes = host_sets[0][4].numel() * host_sets[0][4].element_size() * layers * world
+
+    def e2e_step():
+        for i in range(layers):
+            hq, hk, hv, kv_len, ho = host_sets[i % n_host]
+            dq, dk, dv, do = dev_bufs[i % 2]
+            with torch.cuda.stream(copy_in):
+                copy_in.wait_event(buf_free[i % 2])
+                dq.copy_(hq, non_blocking=True)
+                dk.copy_(hk, non_blocking=True)
+                dv.copy_(hv, non_blocking=True)
+                in_ready[i % 2].record(copy_in)
+            compute.wait_event(in_ready[i % 2])
+            if mode == "local":
+                dtb200.attention(dq, dk, dv, kv_len=kv_len, use_fixed_m=args.fixed_m, out=do)
+            elif mode == "ulysses":
+                parallel.ulysses_attention(dq, dk, dv, kv_len=kv_len, out=do)
+            else:
+                parallel.ring_attention(dq, dk, dv, kv_len=kv_len, out=do)
+            out_ready[i % 2].record(compute)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(out_ready[i % 2])
+                ho.copy_(do, non_blocking=True)
+                buf_free[i % 2].record(copy_out)
+        compute.wait_stream(copy_out)
+
+    for ev in buf_free:
+        ev.record(compute)
+    e2e_steps = max(1, min(args.steps, 3))
+    e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+    dtb200.check_device_status(dev)
+
+    if world > 1:
+        t = torch.tensor([ms_total, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms = t.tolist()
+
+    flops_call = cfg.flops()
+    flops_step = flops_call * layers
+    value = flops_step * args.steps / (ms_total * 1e-3) / 1e12
+    e2e_value = flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    burst, sustained, src = measured_peaks()
+    # dominant kernel: attn_fwd_kernel, one launch per layer call per rank; its share of the call's FLOPs
+    flops_launch = flops_call / world
+    launch_ms = ms_total / (args.steps * layers)
+    achieved = flops_launch / (launch_ms * 1e-3) / 1e12
+
+    cpu_base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_base, _ = cpu_attention_sample(cfg, min(cfg.heads, 8 if cfg.seq <= 8192 else 1), 10.0, 12)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total / args.steps, "ms_per_layer_call": launch_ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": cfg.name, "B": cfg.batch, "H": cfg.heads, "S": cfg.seq, "D": cfg.head_dim,
+                "layer_calls_per_step": layers, "softmax": "bounded-logit (fixed-m)" if args.fixed_m else "online",
+                "parallelism": {"local": f"cfg{bg}xheads{hg} (resident head-parallel shards, no collective)",
+                                "ulysses": f"ulysses{world} (all-to-all)", "ring": f"ring{world} (KV rotation)"}[mode],
+                "l2": "inputs larger than L2: every layer call reads its own q/k/v buffers "
+                      f"({layers} sets, {3 * sets[0][0].numel() * 2 / 1e6:.0f} MB each per rank)",
+                "inputs": "N(0,1) q,k,v with unit-weight qk-RMSNorm, bf16, trailing text padding 0-300 keys per batch element",
+            },
+            "pct_of_peak": {"of_measured_burst": 100 * value / (burst * world), "of_nominal_2250": 100 * value / (2250.0 * world)},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
+                         "frac_of_sustained": achieved / sustained, "peak_source": f"{src} burst bf16 GEMM",
+                         "kernel": "attn_fwd_kernel", "flops_per_launch": flops_launch,
+                         "traffic": NCU_TRAFFIC_BYTES_C2 if cfg.name == "c2_image1024" and world == 1 else None},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                    "how": "pinned host q,k,v -> device (double buffered, copy streams) -> dtb200.attention -> pinned host o"},
+            "gpu_launches": args.steps * layers * launches_per_call,
+            "clocks": clocks,
+            "cpu_baseline": cpu_base,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2_image1024")
+    ap.add_argument("--mode", default="auto", choices=["auto", "local", "ulysses", "ring"])
+    ap.add_argument("--layers", type=int, default=0, help="layer calls per step (default: per workload)")
+    ap.add_argument("--fixed-m", action="store_true", help="bounded-logit softmax, operand derived per call")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    from dtb200.inputs import CONFIGS
+
+    cfg = CONFIGS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

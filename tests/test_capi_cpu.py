@@ -1,0 +1,97 @@
+"""CPU-side checks of the C-ABI library: it builds, loads, exports every symbol the public header
+declares, and validates arguments without needing a GPU (no compute call is made here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from dtb200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "dtb200_attn.h")
+
+
+def _declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dtb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    declared = _declared_functions()
+    assert declared, "no declarations found in the header"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/dtb200_attn.h but not exported"
+    assert sorted(_lib.EXPORTED_SYMBOLS) == declared
+
+
+def test_struct_layout_matches_header():
+    # 4 pointers, 6 int32, 12 int64, 2 pointers, float, uint32, int32, (pad), pointer
+    assert ctypes.sizeof(_lib.AttnParams) == 4 * 8 + 6 * 4 + 12 * 8 + 2 * 8 + 4 + 4 + 4 + 4 + 8
+    assert ctypes.sizeof(_lib.AttnResidual) == 3 * 8 + 3 * 4 + 4
+
+
+def _params(**kw):
+    p = _lib.AttnParams()
+    p.q = p.k = p.v = p.o = 4096
+    p.B, p.Hq, p.Hkv, p.Sq, p.Skv, p.D = 1, 4, 4, 512, 512, 128
+    p.q_stride_s = p.k_stride_s = p.v_stride_s = p.o_stride_s = 128
+    p.q_stride_h = p.k_stride_h = p.v_stride_h = p.o_stride_h = 512 * 128
+    p.q_stride_b = p.k_stride_b = p.v_stride_b = p.o_stride_b = 4 * 512 * 128
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("kw,code", [
+    ({"D": 64}, 3),                 # head_dim other than 128
+    ({"Hkv": 3}, 3),                # query heads not a multiple of kv heads
+    ({"Sq": 0}, 3),
+    ({"q": None}, 1),
+    ({"o": 4100}, 4),               # output pointer not 16-byte aligned
+    ({"o_stride_s": 132}, 4),       # output row stride not a multiple of 16 bytes
+    ({"flags": _lib.FLAG_BOUNDED_LOGITS}, 1),   # bounded-logit mode without its operand
+])
+def test_argument_validation_without_a_device(kw, code):
+    lib = _lib.load()
+    why = ctypes.c_int(-1)
+    assert lib.dtb_attn_supported(ctypes.byref(_params(**kw)), ctypes.byref(why)) == 0
+    assert why.value == code
+    assert lib.dtb_attn_fwd(ctypes.byref(_params(**kw)), None, 0, None) == code
+
+
+def test_workspace_query_and_status_strings():
+    lib = _lib.load()
+    assert lib.dtb_version() >= 100
+    assert lib.dtb_attn_workspace_bytes(ctypes.byref(_params())) == 0            # 2 q-blocks x 4 heads, short keys
+    p = _params(Sq=128, Skv=8192, num_splits=4)
+    assert lib.dtb_attn_workspace_bytes(ctypes.byref(p)) == 4 * 1 * 4 * 128 * (128 + 2) * 4
+    p = _params(Sq=128, Skv=8192, num_splits=0, Hq=2, Hkv=2)                      # automatic split for a short-query call
+    assert lib.dtb_attn_workspace_bytes(ctypes.byref(p)) > 0
+    for code, name in _lib.STATUS_NAMES.items():
+        assert _lib.status_string(code)
+    assert _lib.status_string(12345) == "unknown status"
+
+
+def test_status_maps_to_reference_exception_types():
+    with pytest.raises(NotImplementedError):
+        _lib.check(3, "x")
+    with pytest.raises(ValueError):
+        _lib.check(4, "x")
+    with pytest.raises(RuntimeError):
+        _lib.check(7, "x")
+    _lib.check(0, "x")
+
+
+def test_python_api_refuses_cpu_tensors():
+    import torch
+
+    import dtb200
+
+    q = torch.zeros(1, 2, 128, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        dtb200.attention(q, q, q)
+    with pytest.raises(ValueError, match="use_fixed_m needs"):
+        dtb200.residual_attention(q, q, q, use_fixed_m=True)
