@@ -116,17 +116,6 @@ def dist_env():
     return rank, world, local
 
 
-def placement(batch: int, heads: int, world: int):
-    """CFG halves on chip halves, then heads: returns (batch_groups, head_groups)."""
-    bg = min(batch, world)
-    while world % bg:
-        bg -= 1
-    hg = world // bg
-    if heads % hg:
-        raise SystemExit(f"{heads} heads do not divide over {hg} ranks per batch group; use --mode ring")
-    return bg, hg
-
-
 # --------------------------------------------------------------------------------------------
 # reference arm: the oracle's fp32-softmax attention on the host cores
 # --------------------------------------------------------------------------------------------
@@ -200,9 +189,9 @@ def run_ours(args, cfg):
     if mode == "auto":
         mode = "local"
     layers = args.layers or LAYERS[cfg.name]
-    if mode != "local":
-        from dtb200 import parallel
-    bg, hg = placement(cfg.batch, cfg.heads, world) if mode == "local" else (1, 1)
+    from dtb200 import parallel
+
+    bg, hg = parallel.placement(cfg.batch, cfg.heads, world) if mode == "local" else (1, 1)
     b_local = cfg.batch // bg
     h_local = cfg.heads // hg
     my_b = (rank // hg) * b_local
