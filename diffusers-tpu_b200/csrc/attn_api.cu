@@ -4,6 +4,8 @@
 #include <algorithm>
 #include <atomic>
 #include <cmath>
+#include <cstdio>
+#include <mutex>
 
 #include "attn_kernel.cuh"
 #include "host_common.h"
@@ -302,4 +304,85 @@ extern "C" int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float*
       norms + p->Hq);
   fixed_m_finish_kernel<<<(p->Hq + 127) / 128, 128, 0, s>>>(norms, p->Hq, p->Hkv, gate, mk_out);
   return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Split-KV forward for callers that cannot hand over scratch memory.
+//
+// The partial (o, m, l) states live in a fixed array inside the library image instead of a
+// caller-provided workspace.  Every device that loads the library carries the array until the
+// process exits.  All calls on a device share it, so two calls whose kernels may overlap on that
+// device (different streams, different threads) race on it; callers must order such calls.  Nothing in
+// the array needs clearing between calls: the partial kernel writes every (split, row) slot the
+// combine kernel reads, empty splits included.
+// ---------------------------------------------------------------------------------------------
+namespace dtb {
+namespace {
+
+static __device__ __align__(256) unsigned char g_static_scratch[DTB_STATIC_SCRATCH_BYTES];
+
+std::mutex g_static_scratch_mu;
+void* g_static_scratch_ptr[64] = {};
+
+// Device address of the array on the current device.  In host code `g_static_scratch` is only a
+// handle for the runtime, not an address a kernel may use; the address is looked up once per device
+// (with that device current) and cached.
+int static_scratch_address(void** out) {
+  int dev = 0;
+  if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return DTB_ERR_LAUNCH;
+  if (dev < 0 || dev >= 64) return DTB_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (!cuda_ok(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress(static scratch)"))
+      return DTB_ERR_LAUNCH;
+    if (ptr == nullptr) return DTB_ERR_LAUNCH;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return DTB_OK;
+}
+
+}  // namespace
+}  // namespace dtb
+
+extern "C" int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* stream) {
+  int st = check_params(p, true);
+  if (st != DTB_OK) return st;
+  if (!device_is_sm100()) return DTB_ERR_ARCH;
+  const int splits = resolve_splits(p);
+  const size_t need = splits > 1 ? split_workspace_bytes(p, splits) : 0;
+  if (need > static_cast<size_t>(DTB_STATIC_SCRATCH_BYTES)) {
+    char msg[200];
+    snprintf(msg, sizeof(msg), "split-KV partials need %zu bytes, the built-in scratch holds %zu", need,
+             static_cast<size_t>(DTB_STATIC_SCRATCH_BYTES));
+    set_detail(msg);
+    return DTB_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  st = static_scratch_address(&scratch);
+  if (st != DTB_OK) return st;
+  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
+  AttnKernelParams kp;
+  st = fill_kernel_params(p, &kp);
+  if (st != DTB_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 block(kNumThreads);
+  if (splits == 1) {
+    attn_fwd_kernel<false><<<dim3(q_blocks(p), p->Hq, p->B), block, kSmemBytes, s>>>(kp);
+    return launch_ok("attn_fwd_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
+  }
+  const size_t rows = static_cast<size_t>(splits) * p->B * p->Hq * p->Sq;
+  kp.acc_o = static_cast<float*>(scratch);
+  kp.acc_m = kp.acc_o + rows * kHeadDim;
+  kp.acc_l = kp.acc_m + rows;
+  kp.num_splits = splits;
+  kp.acc_init = 1;
+  attn_fwd_kernel<true><<<dim3(q_blocks(p), p->Hq, p->B * splits), block, kSmemBytes, s>>>(kp);
+  if (!launch_ok("attn_fwd_kernel launch")) return DTB_ERR_LAUNCH;
+  const int64_t out_rows = static_cast<int64_t>(p->B) * p->Hq * p->Sq;
+  combine_kernel<<<static_cast<unsigned>((out_rows + 7) / 8), 256, 0, s>>>(
+      kp.acc_o, kp.acc_m, kp.acc_l, splits, p->B, p->Hq, p->Sq, kp.o, kp.o_stride_b, kp.o_stride_h, kp.o_stride_s,
+      p->kv_len, 0, kp.zero_padded_rows);
+  return launch_ok("combine_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }

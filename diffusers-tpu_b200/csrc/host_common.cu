@@ -20,6 +20,8 @@ bool launch_ok(const char* what) { return cuda_ok(cudaGetLastError(), what); }
 
 const char* last_detail() { return g_detail; }
 
+void set_detail(const char* text) { snprintf(g_detail, sizeof(g_detail), "%s", text); }
+
 EncodeTiledFn get_encode_tiled() {
   static EncodeTiledFn fn = nullptr;
   static std::once_flag once;

@@ -31,6 +31,8 @@ bool cuda_ok(cudaError_t e, const char* what);
 // Checks (and clears) the launch error of the kernel just enqueued.
 bool launch_ok(const char* what);
 const char* last_detail();
+// Sets the text dtb_last_error_detail() returns for the calling thread.
+void set_detail(const char* text);
 
 // True when the current device is compute capability 10.x.
 bool device_is_sm100();

@@ -20,11 +20,12 @@ STATUS_NAMES = {
 
 FLAG_ZERO_PADDED_ROWS = 0x1
 FLAG_BOUNDED_LOGITS = 0x2
+STATIC_SCRATCH_BYTES = 32 << 20
 
 # Every symbol the public header declares; tests check that the library exports all of them.
 EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
-    "dtb_attn_fwd", "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands",
+    "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands",
     "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv",
 )
 
@@ -86,6 +87,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         lib.dtb_attn_workspace_bytes.argtypes = [ctypes.POINTER(AttnParams)]
         lib.dtb_attn_fwd.restype = ctypes.c_int
         lib.dtb_attn_fwd.argtypes = [ctypes.POINTER(AttnParams), vp, ctypes.c_size_t, vp]
+        lib.dtb_attn_fwd_static_scratch.restype = ctypes.c_int
+        lib.dtb_attn_fwd_static_scratch.argtypes = [ctypes.POINTER(AttnParams), vp]
         lib.dtb_attn_fwd_residual.restype = ctypes.c_int
         lib.dtb_attn_fwd_residual.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnResidual), vp]
         lib.dtb_attn_finalize.restype = ctypes.c_int

@@ -104,6 +104,22 @@ int dtb_attn_finalize(const dtb_attn_params* p, const dtb_attn_residual* r, void
  * diffusers_tpu/kernels/fixed_m_bound.py:57-118 `max_row_norm_per_head` + `fixed_m_operands`. */
 int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float* norms, float* mk_out, void* stream);
 
+/* Bytes of scratch built into the library image for dtb_attn_fwd_static_scratch (32 MiB per device). */
+#define DTB_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* Same result as dtb_attn_fwd, for callers that have nowhere to get scratch memory from: a handler
+ * running inside another runtime's execution callback (an XLA FFI custom call, a graph node, a plugin
+ * of a serving engine) or a foreign-language binding that only ever sees the input and output buffers
+ * it was given.  Such callers must not call cudaMalloc themselves and cannot pass a workspace, so the
+ * split-KV partials are kept in a fixed DTB_STATIC_SCRATCH_BYTES array that is part of the library and
+ * stays resident on every device that loads it.  The call allocates nothing.  Calls whose partials
+ * would not fit return DTB_ERR_WORKSPACE (dtb_last_error_detail() gives both sizes); p->num_splits
+ * is honoured as in dtb_attn_fwd.  The first call on each device looks up the array's device address;
+ * make that first call outside any stream capture.  All calls on a device share the array: calls that
+ * may overlap on the GPU race and must be ordered by the caller.
+ * This entry point has no counterpart in the reference project. */
+int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* stream);
+
 /* Hardware self-tests of the descriptor encodings the kernels rely on (one 128x128x128 tile each).
  * They write f32 [128,128] results for the host to compare; no reference counterpart. */
 int dtb_selftest_tmem_roundtrip(const float* in, float* out, int32_t* status, void* stream);
