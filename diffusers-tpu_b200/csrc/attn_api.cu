@@ -386,3 +386,13 @@ extern "C" int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* strea
       p->kv_len, 0, kp.zero_padded_rows);
   return launch_ok("combine_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
+
+#ifdef DTB_PROFILE_WAITS
+// Diagnostic builds only: copies out and clears the wait-time counters (32 x uint64).
+extern "C" int dtb_debug_read_wait_profile(unsigned long long* out) {
+  if (cudaMemcpyFromSymbol(out, dtb::g_wait_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return DTB_ERR_LAUNCH;
+  unsigned long long zeros[32] = {};
+  if (cudaMemcpyToSymbol(dtb::g_wait_prof, zeros, sizeof(zeros)) != cudaSuccess) return DTB_ERR_LAUNCH;
+  return DTB_OK;
+}
+#endif

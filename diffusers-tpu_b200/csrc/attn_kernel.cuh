@@ -11,8 +11,9 @@
 //               (each SM sub-partition holds 16384 registers shared by one warp of each group).
 //
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 f32 columns each.  P (bf16)
-// is written over the first 64 columns of its S tile and consumed from tensor
-// memory by the PV MMA, so probabilities never touch shared memory.
+// is written over the first 64 columns of its S tile (in two halves, each with its
+// own mbarrier) and consumed from tensor memory by the PV MMA, so probabilities never
+// touch shared memory.
 //
 // Shared memory: Q (2 x 32 KB, loaded once) and a ring of 32 KB slots through
 // which K_0, V_0, K_1, V_1, ... flow; every tile is two 64-column panels written
@@ -47,14 +48,40 @@ constexpr int kRegsService = 56;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units: rescale O only when the row max grew by > 2^8
 constexpr float kFixedMRecenter = 88.0f;     // bounded-logit mode exponent offset (m - 88)
+// Of every four consecutive key pairs, this many take the FMA-pipe polynomial exp2 instead of the
+// MUFU unit, which otherwise is as busy as the tensor core (one ex2 per score).
+#ifndef DTB_EXP2_POLY_QUARTERS
+#define DTB_EXP2_POLY_QUARTERS 0
+#endif
+constexpr int kExp2PolyQuarters = DTB_EXP2_POLY_QUARTERS;
+
+// Optional wait-time accounting (a diagnostic build, -DDTB_PROFILE_WAITS): cycles spent in each kind of
+// barrier wait, summed over CTAs, readable through dtb_debug_read_wait_profile().
+#ifdef DTB_PROFILE_WAITS
+__device__ unsigned long long g_wait_prof[32];
+#define DTB_PROF_DECL long long prof_t = 0; long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define DTB_PROF_BEGIN() prof_t = clock64()
+#define DTB_PROF_END(slot) prof_acc[slot] += clock64() - prof_t
+#define DTB_PROF_FLUSH(base, cond)                                                         \
+  if (cond) {                                                                              \
+    for (int i_ = 0; i_ < 8; ++i_) atomicAdd(&g_wait_prof[(base) + i_], (unsigned long long)prof_acc[i_]); \
+  }
+#else
+#define DTB_PROF_DECL
+#define DTB_PROF_BEGIN()
+#define DTB_PROF_END(slot)
+#define DTB_PROF_FLUSH(base, cond)
+#endif
 
 struct __align__(8) PipelineBarriers {
   uint64_t q_full[kQTiles];
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
   uint64_t s_full[kQTiles];
-  uint64_t p_full[kQTiles];
+  uint64_t p_lo[kQTiles];   // first 64 keys of P_t written
+  uint64_t p_hi[kQTiles];   // last 64 keys of P_t written
   uint64_t o_full[kQTiles];
+  uint64_t turn[kQTiles];   // MUFU turn-taking between the two softmax groups
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -64,7 +91,7 @@ constexpr size_t kSmemBytes = 1024 /* alignment slack */ + kQTiles * kTileBytes 
 
 // Barrier-site ids reported in status[1] when a wait runs out.
 enum WaitSite : int {
-  SITE_Q_FULL = 10, SITE_KV_FULL = 20, SITE_KV_EMPTY = 30, SITE_S_FULL = 40, SITE_P_FULL = 50, SITE_O_FULL = 60
+  SITE_Q_FULL = 10, SITE_KV_FULL = 20, SITE_KV_EMPTY = 30, SITE_S_FULL = 40, SITE_P_FULL = 50, SITE_P_HI = 55, SITE_O_FULL = 60, SITE_TURN = 70
 };
 
 struct AttnKernelParams {
@@ -93,37 +120,51 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, const 
 }
 
 // ---------------------------------------------------------------------------
-// One key tile of online softmax for the row owned by this thread.
+// One key tile of softmax for the row owned by this thread.
+//
+// The whole S row comes out of tensor memory in one load; the row max uses three-input max; the
+// scale-and-subtract and the row sum run on packed f32 pairs; P goes back to tensor memory in two
+// halves of 64 keys, each published on its own mbarrier so the PV MMA of the first half runs while
+// the second half is still being exponentiated.
 // ---------------------------------------------------------------------------
 template <bool kFixedM>
 __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, float scale_log2, int valid_cols,
-                                             bool o_live, float& m_used, float& l_sum) {
-  float s[kBlockN];
-  {
-    uint32_t r[32];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      tmem_ld32(s_tmem + c * 32, r);
-      tmem_wait_ld();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
-    }
+                                             bool o_live, float& m_used, float& l_sum, uint32_t bar_p_lo,
+                                             uint32_t bar_p_hi, uint64_t* my_turn, uint32_t turn_parity,
+                                             uint32_t other_turn, const AbortCtx& ctx, int site, bool& ok) {
+  uint32_t sr[kBlockN];
+#ifdef DTB_PROFILE_WAITS
+  const bool prof_on = (threadIdx.x & 127) == 0;
+  const int prof_base = 8 + 8 * (threadIdx.x >> 7);
+  long long pt = clock64();
+#define DTB_PROF_LAP(slot)                                                              \
+  {                                                                                     \
+    const long long now_ = clock64();                                                   \
+    if (prof_on) atomicAdd(&g_wait_prof[prof_base + (slot)], (unsigned long long)(now_ - pt)); \
+    pt = clock64();                                                                     \
   }
+#else
+#define DTB_PROF_LAP(slot)
+#endif
+  tmem_ld128_sync(s_tmem, sr);
+  DTB_PROF_LAP(2);
   if (valid_cols < kBlockN) {
 #pragma unroll
     for (int i = 0; i < kBlockN; ++i)
-      if (i >= valid_cols) s[i] = -INFINITY;
+      if (i >= valid_cols) sr[i] = 0xff800000u;  // -inf
   }
   if (!kFixedM) {
-    float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+    // eight independent chains of three-input max keep the dependency depth at 8 + 3
+    float mxs[8];
 #pragma unroll
-    for (int i = 4; i < kBlockN; i += 4) {
-      mx0 = fmaxf(mx0, s[i]);
-      mx1 = fmaxf(mx1, s[i + 1]);
-      mx2 = fmaxf(mx2, s[i + 2]);
-      mx3 = fmaxf(mx3, s[i + 3]);
+    for (int c = 0; c < 8; ++c) mxs[c] = fmaxf(__uint_as_float(sr[c]), __uint_as_float(sr[c + 8]));
+#pragma unroll
+    for (int i = 16; i < kBlockN; i += 16) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) mxs[c] = max3(mxs[c], __uint_as_float(sr[i + c]), __uint_as_float(sr[i + c + 8]));
     }
-    const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+    const float mx = fmaxf(max3(mxs[0], mxs[1], mxs[2]), fmaxf(max3(mxs[3], mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7]))) *
+                     scale_log2;
     const bool grow = mx > m_used + kRescaleThreshold;  // always true while m_used == -inf
     if (o_live && __any_sync(0xffffffffu, grow)) {
       const float alpha = grow ? ex2(m_used - mx) : 1.0f;
@@ -131,8 +172,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
       uint32_t r[32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        tmem_ld32(o_tmem + c * 32, r);
-        tmem_wait_ld();
+        tmem_ld32_sync(o_tmem + c * 32, r);
 #pragma unroll
         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
         tmem_st32(o_tmem + c * 32, r);
@@ -144,23 +184,53 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
     }
     if (grow) m_used = mx;
   }
-  const float neg_m = -m_used;
-  float acc0 = 0.f, acc1 = 0.f;
+  // The exponentials of the two groups take turns: alone, a group's 128 x 128 ex2 saturate the MUFU
+  // unit of each SM sub-partition for as long as the tensor core needs for the other group's
+  // P*V and next Q*K^T, so strict alternation keeps both units busy; in lock-step they would halve
+  // each other's rate and then both wait for the tensor core.
+  DTB_PROF_LAP(3);
+#ifdef DTB_PROFILE_WAITS
+  const long long turn_t0 = clock64();
+#endif
+  ok = warp_wait(my_turn, turn_parity, ctx, site);
+#ifdef DTB_PROFILE_WAITS
+  if ((threadIdx.x & 127) == 0) atomicAdd(&g_wait_prof[30 + (threadIdx.x >> 7)], (unsigned long long)(clock64() - turn_t0));
+#endif
+  if (!ok) return;
+#ifdef DTB_PROFILE_WAITS
+  pt = clock64();
+#endif
+  const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+  const uint64_t neg_m2 = pack_f32x2(-m_used, -m_used);
+  uint64_t acc2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t pk[16];
+  for (int half = 0; half < 2; ++half) {
+    uint32_t pk[32];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float p0 = ex2(fmaf(s[c * 32 + 2 * i], scale_log2, neg_m));
-      const float p1 = ex2(fmaf(s[c * 32 + 2 * i + 1], scale_log2, neg_m));
-      acc0 += p0;
-      acc1 += p1;
+    for (int i = 0; i < 32; ++i) {
+      const int col = half * 64 + 2 * i;
+      const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sr[col]), __uint_as_float(sr[col + 1])), scale2, neg_m2);
+      float x0, x1, p0, p1;
+      unpack_f32x2(x2, x0, x1);
+      if ((i & 3) < kExp2PolyQuarters) {
+        ex2_poly_f32x2(pack_f32x2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f)), p0, p1);
+      } else {
+        p0 = ex2(x0);
+        p1 = ex2(x1);
+      }
+      acc2 = add_f32x2(acc2, pack_f32x2(p0, p1));
       pk[i] = pack_bf16x2(p0, p1);
     }
-    tmem_st16(s_tmem + c * 16, pk);
+    tmem_st32(s_tmem + half * 32, pk);
+    tmem_wait_st();
+    tc_fence_before();
+    mbar_arrive(half == 0 ? bar_p_lo : bar_p_hi);
+    DTB_PROF_LAP(4 + half);
   }
-  l_sum += acc0 + acc1;
-  tmem_wait_st();
+  mbar_arrive(other_turn);
+  float a0, a1;
+  unpack_f32x2(acc2, a0, a1);
+  l_sum += a0 + a1;
 }
 
 // ---------------------------------------------------------------------------
@@ -228,8 +298,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     for (int i = 0; i < kQTiles; ++i) {
       mbar_init(smem_u32(&bars->q_full[i]), 1);
       mbar_init(smem_u32(&bars->s_full[i]), 1);
-      mbar_init(smem_u32(&bars->p_full[i]), kBlockM);
+      mbar_init(smem_u32(&bars->p_lo[i]), kBlockM);
+      mbar_init(smem_u32(&bars->p_hi[i]), kBlockM);
       mbar_init(smem_u32(&bars->o_full[i]), 1);
+      mbar_init(smem_u32(&bars->turn[i]), kBlockM);
     }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(smem_u32(&bars->kv_full[i]), 1);
@@ -255,6 +327,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     // ------------------------------------------------------------------ TMA producer
     setmaxnreg_dec<kRegsService>();
     bool ok = true;
+    DTB_PROF_DECL;
     if (lane == 0) {
       for (int t = 0; t < kQTiles; ++t) {
         const uint32_t bar = smem_u32(&bars->q_full[t]);
@@ -266,7 +339,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       for (int i = 0; i < 2 * n_tiles && ok; ++i) {
         const int slot = i % kStages;
         const int use = i / kStages;
+        DTB_PROF_BEGIN();
         if (use > 0) ok = mbar_wait(smem_u32(&bars->kv_empty[slot]), (use - 1) & 1, ctx, SITE_KV_EMPTY + slot);
+        DTB_PROF_END(0);
         if (!ok) break;
         const uint32_t bar = smem_u32(&bars->kv_full[slot]);
         mbar_expect_tx(bar, kTileBytes);
@@ -276,6 +351,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         tma_load_4d(dst, tm, bar, 0, row, hk, b);
         tma_load_4d(dst + kPanelBytes, tm, bar, 64, row, hk, b);
       }
+      DTB_PROF_FLUSH(24, true);
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
@@ -287,6 +363,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem_kv), 16, 1024);
     const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem_kv), kPanelBytes, 1024);
     bool ok = true;
+    DTB_PROF_DECL;
+    const long long prof_start = clock64();
 
     auto issue_qk = [&](int t, int slot) {
       if (lane == 0) {
@@ -301,13 +379,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       }
       __syncwarp();
     };
-    auto issue_pv = [&](int t, int slot, bool accumulate) {
+    auto issue_pv = [&](int t, int slot, int half, bool accumulate) {
       if (lane == 0) {
         const uint64_t b0 = v_desc0 + static_cast<uint64_t>((slot * kTileBytes) >> 4);
         const uint32_t d_tmem = tmem_base + (kQTiles + t) * kBlockN;
         const uint32_t a_tmem = tmem_base + t * kBlockN;
 #pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+        for (int kk = half * 4; kk < half * 4 + 4; ++kk) {
           const uint64_t off = static_cast<uint64_t>((kk * 16 * 128) >> 4);
           mma_ts(d_tmem, a_tmem + kk * 8, b0 + off, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
         }
@@ -340,16 +418,28 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int iv = 2 * j + 1;
       const int ik = 2 * j + 2;
+      DTB_PROF_BEGIN();
       ok = wait_kv(iv);
+      DTB_PROF_END(0);
       for (int t = 0; t < kQTiles && ok; ++t) {
-        ok = warp_wait(&bars->p_full[t], j & 1, ctx, SITE_P_FULL + t);
+        DTB_PROF_BEGIN();
+        ok = warp_wait(&bars->p_lo[t], j & 1, ctx, SITE_P_FULL + t);
+        DTB_PROF_END(2 + t);
         if (!ok) break;
         tc_fence_after();
-        issue_pv(t, iv % kStages, j > 0 || o_preloaded);
+        issue_pv(t, iv % kStages, 0, j > 0 || o_preloaded);
+        DTB_PROF_BEGIN();
+        ok = warp_wait(&bars->p_hi[t], j & 1, ctx, SITE_P_HI + t);
+        DTB_PROF_END(4 + t);
+        if (!ok) break;
+        tc_fence_after();
+        issue_pv(t, iv % kStages, 1, true);
         if (t == kQTiles - 1) commit_to(&bars->kv_empty[iv % kStages]);
         if (j + 1 < n_tiles) {
           if (t == 0) {
+            DTB_PROF_BEGIN();
             ok = wait_kv(ik);
+            DTB_PROF_END(1);
             if (!ok) break;
             tc_fence_after();
           }
@@ -360,6 +450,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         }
       }
     }
+#ifdef DTB_PROFILE_WAITS
+    prof_acc[6] = clock64() - prof_start;
+    prof_acc[7] = n_tiles;
+#endif
+    DTB_PROF_FLUSH(0, lane == 0);
   } else if (warp < kMmaWarp) {
     // ------------------------------------------------------------------ softmax groups
     setmaxnreg_inc<kRegsSoftmax>();
@@ -372,6 +467,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     const float scale_log2 = p.scale_log2;
     const bool row_in_range = row < p.Sq;
     const int64_t acc_row = unit * p.Sq + row;
+    const uint32_t bar_p_lo = smem_u32(&bars->p_lo[t]);
+    const uint32_t bar_p_hi = smem_u32(&bars->p_hi[t]);
+    const uint32_t other_turn = smem_u32(&bars->turn[t ^ 1]);
+    if (t == 1) mbar_arrive(smem_u32(&bars->turn[0]));  // group 0 exponentiates first
 
     float m_used = -INFINITY;
     float l_sum = 0.f;
@@ -414,8 +513,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           uint32_t r[32];
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            tmem_ld32(o_tmem + c * 32, r);
-            tmem_wait_ld();
+            tmem_ld32_sync(o_tmem + c * 32, r);
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
             tmem_st32(o_tmem + c * 32, r);
@@ -429,21 +527,34 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     }
 
     bool ok = true;
+    DTB_PROF_DECL;
+#ifdef DTB_PROFILE_WAITS
+    const long long prof_start = clock64();
+#endif
     for (int j = 0; j < n_tiles && ok; ++j) {
+      DTB_PROF_BEGIN();
       ok = warp_wait(&bars->s_full[t], j & 1, ctx, SITE_S_FULL + t);
+      DTB_PROF_END(0);
       if (!ok) break;
       tc_fence_after();
       const int valid_cols = min(kv_eff - (tile_begin + j) * kBlockN, kBlockN);
       if (fixed_m) {
-        softmax_tile<true>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum);
+        softmax_tile<true>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum, bar_p_lo, bar_p_hi,
+                           &bars->turn[t], j & 1, other_turn, ctx, SITE_TURN + t, ok);
       } else {
-        softmax_tile<false>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum);
+        softmax_tile<false>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum, bar_p_lo, bar_p_hi,
+                            &bars->turn[t], j & 1, other_turn, ctx, SITE_TURN + t, ok);
       }
+      if (!ok) break;
       o_live = true;
-      tc_fence_before();
-      mbar_arrive(smem_u32(&bars->p_full[t]));
     }
+    DTB_PROF_BEGIN();
     if (ok) ok = warp_wait(&bars->o_full[t], 0, ctx, SITE_O_FULL + t);
+    DTB_PROF_END(1);
+#ifdef DTB_PROFILE_WAITS
+    prof_acc[6] = clock64() - prof_start;
+#endif
+    DTB_PROF_FLUSH(8 + 8 * t, (threadIdx.x & 127) == 0);
     if (ok) {
       tc_fence_after();
       if (kResidual) {
@@ -451,8 +562,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
-          tmem_ld32(o_tmem + c * 32, r);
-          tmem_wait_ld();
+          tmem_ld32_sync(o_tmem + c * 32, r);
           if (row_in_range) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -471,8 +581,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
-          tmem_ld32(o_tmem + c * 32, r);
-          tmem_wait_ld();
+          tmem_ld32_sync(o_tmem + c * 32, r);
           if (row_in_range) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {

@@ -166,6 +166,74 @@ __global__ void __launch_bounds__(128) mma_tile_kernel(const __grid_constant__ C
   if (warp == 0) tmem_dealloc(tbase, 256);
 }
 
+// Tensor-pipe rate probe: one CTA issues `iters` rounds of 8 back-to-back MMAs (one 128-deep
+// contraction) on garbage operands and reports the cycles from first issue to completion.
+//   mode 0: SS 128x128x16   mode 1: SS 128x64x16   mode 2: TS 128x128x16 (A in tensor memory)
+//   mode 3: SS 128x256x16
+__global__ void __launch_bounds__(128) mma_rate_kernel(int mode, int iters, long long* out, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ SelftestShared sh;
+  uint8_t* smem = align_1024(smem_raw);
+  const int warp = threadIdx.x >> 5;
+  AbortCtx ctx{&sh.abort_flag, status};
+  if (threadIdx.x == 0) {
+    sh.abort_flag = 0;
+    mbar_init(smem_u32(&sh.bar_mma), 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&sh.tmem_base), 512);
+    tmem_relinquish();
+  }
+  // finite operands: zero the shared tiles (A 32 KB, B 64 KB)
+  for (int i = threadIdx.x; i < (96 * 1024) / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = sh.tmem_base;
+  {
+    uint32_t z[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) z[i] = 0;
+    for (int c = 0; c < 16; ++c) tmem_st32(tbase + (static_cast<uint32_t>(warp * 32) << 16) + c * 32, z);
+    tmem_wait_st();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    tc_fence_after();
+    const int n = mode == 1 ? 64 : (mode == 3 ? 256 : 128);
+    const uint32_t idesc = make_idesc_bf16(128, n, false, mode == 2);
+    const uint64_t a0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
+    const uint64_t b0 = mode == 2 ? make_smem_desc_sw128(smem_u32(smem + 32768), kPanelBytes, 1024)
+                                  : make_smem_desc_sw128(smem_u32(smem + 32768), 16, 1024);
+    const long long t0 = clock64();
+    for (int it = 0; it < iters; ++it) {
+      const uint32_t d = tbase + ((it & 1) ? 256u : 0u);   // alternate accumulators
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        if (mode == 2) {
+          mma_ts(d, tbase + 448 + kk * 8, b0 + static_cast<uint64_t>((kk * 2048) >> 4), idesc, 1u);
+        } else {
+          const uint64_t off = static_cast<uint64_t>(((kk & 3) * 32 + (kk >> 2) * kPanelBytes) >> 4);
+          mma_ss(d, a0 + off, b0 + off, idesc, 1u);
+        }
+      }
+    }
+    mma_commit(smem_u32(&sh.bar_mma));
+    const long long t1 = clock64();
+    const bool ok = mbar_wait(smem_u32(&sh.bar_mma), 0, ctx, 3);
+    const long long t2 = clock64();
+    out[0] = t1 - t0;
+    out[1] = t2 - t0;
+    out[2] = ok ? 1 : 0;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
 int launch_tile_test(int mode, const void* a, const void* b, float* out, int32_t* status, void* stream) {
   if (a == nullptr || b == nullptr || out == nullptr) return DTB_ERR_NULL;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
@@ -205,4 +273,16 @@ extern "C" int dtb_selftest_qk(const void* q, const void* k, float* s_out, int32
 
 extern "C" int dtb_selftest_pv(const void* p, const void* v, float* o_out, int32_t* status, void* stream) {
   return dtb::launch_tile_test(1, p, v, o_out, status, stream);
+}
+
+extern "C" int dtb_selftest_mma_rate(int mode, int iters, long long* out_cycles, int32_t* status, void* stream) {
+  if (out_cycles == nullptr) return DTB_ERR_NULL;
+  if (mode < 0 || mode > 3 || iters <= 0 || iters > 100000) return DTB_ERR_SHAPE;
+  if (!dtb::device_is_sm100()) return DTB_ERR_ARCH;
+  const size_t smem = 96 * 1024 + 1024;
+  if (!dtb::cuda_ok(cudaFuncSetAttribute(dtb::mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                    "cudaFuncSetAttribute"))
+    return DTB_ERR_LAUNCH;
+  dtb::mma_rate_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(mode, iters, out_cycles, status);
+  return dtb::launch_ok("mma_rate_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }

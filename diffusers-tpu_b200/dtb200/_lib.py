@@ -26,7 +26,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
     "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands",
-    "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv",
+    "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_mma_rate",
 )
 
 
@@ -70,7 +70,7 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        path = _build.LIB_PATH
+        path = os.environ.get("DTB200_LIB") or _build.LIB_PATH   # DTB200_LIB selects another build of the library
         if not os.path.exists(path):
             if not build_if_missing:
                 raise RuntimeError(f"{path} is missing; run `python -m dtb200.build`")
@@ -103,6 +103,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.restype = ctypes.c_int
             fn.argtypes = [vp, vp, vp, i32p, vp]
+        lib.dtb_selftest_mma_rate.restype = ctypes.c_int
+        lib.dtb_selftest_mma_rate.argtypes = [ctypes.c_int, ctypes.c_int, vp, i32p, vp]
         _lib = lib
         return lib
 

@@ -41,21 +41,24 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles the library if needed and returns its path."""
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, extra_flags=(), out_path: str = LIB_PATH) -> str:
+    """Compiles the library if needed and returns its path.
+
+    ``extra_flags`` / ``out_path`` build an experimental variant beside the default binary
+    (select it at load time with the ``DTB200_LIB`` environment variable)."""
+    if out_path == LIB_PATH and not force and not _stale():
         return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS]
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra_flags]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [os.path.join(CSRC_DIR, s) for s in SOURCES]
-    cmd += ["-o", LIB_PATH]
+    cmd += ["-o", out_path]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
     if verbose:
         sys.stderr.write(proc.stderr)
-    return LIB_PATH
+    return out_path
 
 
 if __name__ == "__main__":

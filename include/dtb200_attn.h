@@ -125,6 +125,10 @@ int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* stream);
 int dtb_selftest_tmem_roundtrip(const float* in, float* out, int32_t* status, void* stream);
 int dtb_selftest_qk(const void* q, const void* k, float* s_out, int32_t* status, void* stream);
 int dtb_selftest_pv(const void* p, const void* v, float* o_out, int32_t* status, void* stream);
+/* Tensor-pipe rate probe on one SM: `iters` rounds of eight back-to-back 16-deep MMAs.  mode 0: both operands
+ * in shared memory, N = 128; 1: N = 64; 2: A operand in tensor memory, N = 128; 3: N = 256.
+ * out_cycles (device, 3 x int64): cycles spent issuing, cycles until completion, 1 if completed. */
+int dtb_selftest_mma_rate(int mode, int iters, long long* out_cycles, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }
