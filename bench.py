@@ -340,9 +340,14 @@ def run_ours(args, cfg):
                       f"({layers} sets, {3 * sets[0][0].numel() * 2 / 1e6:.0f} MB each per rank)",
                 "inputs": "N(0,1) q,k,v with unit-weight qk-RMSNorm, bf16, trailing text padding 0-300 keys per batch element",
             },
-            "pct_of_peak": {"of_measured_burst": 100 * value / (burst * world), "of_nominal_2250": 100 * value / (2250.0 * world)},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
-                         "frac_of_sustained": achieved / sustained, "peak_source": f"{src} burst bf16 GEMM",
+            "pct_of_peak": {"of_measured_sustained": 100 * value / (sustained * world),
+                            "of_measured_burst": 100 * value / (burst * world),
+                            "of_nominal_2250": 100 * value / (2250.0 * world)},
+            # the kernel is timed inside seconds-long back-to-back steps under the power cap, so the
+            # sustained GEMM figure is the denominator; the fraction of the burst figure is given beside it
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": sustained, "unit": "TFLOP/s",
+                         "frac": achieved / sustained, "frac_of_burst": achieved / burst, "peak_burst": burst,
+                         "peak_source": f"{src} sustained bf16 GEMM (kernel timed inside a long step)",
                          "kernel": "attn_fwd_kernel", "flops_per_launch": flops_launch,
                          "traffic": NCU_TRAFFIC_BYTES_C2 if cfg.name == "c2_image1024" and world == 1 else None},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,

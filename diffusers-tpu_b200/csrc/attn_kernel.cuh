@@ -81,7 +81,6 @@ struct __align__(8) PipelineBarriers {
   uint64_t p_lo[kQTiles];   // first 64 keys of P_t written
   uint64_t p_hi[kQTiles];   // last 64 keys of P_t written
   uint64_t o_full[kQTiles];
-  uint64_t turn[kQTiles];   // MUFU turn-taking between the two softmax groups
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -91,7 +90,7 @@ constexpr size_t kSmemBytes = 1024 /* alignment slack */ + kQTiles * kTileBytes 
 
 // Barrier-site ids reported in status[1] when a wait runs out.
 enum WaitSite : int {
-  SITE_Q_FULL = 10, SITE_KV_FULL = 20, SITE_KV_EMPTY = 30, SITE_S_FULL = 40, SITE_P_FULL = 50, SITE_P_HI = 55, SITE_O_FULL = 60, SITE_TURN = 70
+  SITE_Q_FULL = 10, SITE_KV_FULL = 20, SITE_KV_EMPTY = 30, SITE_S_FULL = 40, SITE_P_FULL = 50, SITE_P_HI = 55, SITE_O_FULL = 60
 };
 
 struct AttnKernelParams {
@@ -130,8 +129,7 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, const 
 template <bool kFixedM>
 __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, float scale_log2, int valid_cols,
                                              bool o_live, float& m_used, float& l_sum, uint32_t bar_p_lo,
-                                             uint32_t bar_p_hi, uint64_t* my_turn, uint32_t turn_parity,
-                                             uint32_t other_turn, const AbortCtx& ctx, int site, bool& ok) {
+                                             uint32_t bar_p_hi) {
   uint32_t sr[kBlockN];
 #ifdef DTB_PROFILE_WAITS
   const bool prof_on = (threadIdx.x & 127) == 0;
@@ -184,22 +182,6 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
     }
     if (grow) m_used = mx;
   }
-  // The exponentials of the two groups take turns: alone, a group's 128 x 128 ex2 saturate the MUFU
-  // unit of each SM sub-partition for as long as the tensor core needs for the other group's
-  // P*V and next Q*K^T, so strict alternation keeps both units busy; in lock-step they would halve
-  // each other's rate and then both wait for the tensor core.
-  DTB_PROF_LAP(3);
-#ifdef DTB_PROFILE_WAITS
-  const long long turn_t0 = clock64();
-#endif
-  ok = warp_wait(my_turn, turn_parity, ctx, site);
-#ifdef DTB_PROFILE_WAITS
-  if ((threadIdx.x & 127) == 0) atomicAdd(&g_wait_prof[30 + (threadIdx.x >> 7)], (unsigned long long)(clock64() - turn_t0));
-#endif
-  if (!ok) return;
-#ifdef DTB_PROFILE_WAITS
-  pt = clock64();
-#endif
   const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
   const uint64_t neg_m2 = pack_f32x2(-m_used, -m_used);
   uint64_t acc2 = pack_f32x2(0.f, 0.f);
@@ -227,7 +209,6 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
     mbar_arrive(half == 0 ? bar_p_lo : bar_p_hi);
     DTB_PROF_LAP(4 + half);
   }
-  mbar_arrive(other_turn);
   float a0, a1;
   unpack_f32x2(acc2, a0, a1);
   l_sum += a0 + a1;
@@ -301,7 +282,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       mbar_init(smem_u32(&bars->p_lo[i]), kBlockM);
       mbar_init(smem_u32(&bars->p_hi[i]), kBlockM);
       mbar_init(smem_u32(&bars->o_full[i]), 1);
-      mbar_init(smem_u32(&bars->turn[i]), kBlockM);
     }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(smem_u32(&bars->kv_full[i]), 1);
@@ -469,8 +449,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     const int64_t acc_row = unit * p.Sq + row;
     const uint32_t bar_p_lo = smem_u32(&bars->p_lo[t]);
     const uint32_t bar_p_hi = smem_u32(&bars->p_hi[t]);
-    const uint32_t other_turn = smem_u32(&bars->turn[t ^ 1]);
-    if (t == 1) mbar_arrive(smem_u32(&bars->turn[0]));  // group 0 exponentiates first
 
     float m_used = -INFINITY;
     float l_sum = 0.f;
@@ -539,13 +517,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       tc_fence_after();
       const int valid_cols = min(kv_eff - (tile_begin + j) * kBlockN, kBlockN);
       if (fixed_m) {
-        softmax_tile<true>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum, bar_p_lo, bar_p_hi,
-                           &bars->turn[t], j & 1, other_turn, ctx, SITE_TURN + t, ok);
+        softmax_tile<true>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum, bar_p_lo, bar_p_hi);
       } else {
-        softmax_tile<false>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum, bar_p_lo, bar_p_hi,
-                            &bars->turn[t], j & 1, other_turn, ctx, SITE_TURN + t, ok);
+        softmax_tile<false>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum, bar_p_lo, bar_p_hi);
       }
-      if (!ok) break;
       o_live = true;
     }
     DTB_PROF_BEGIN();
