@@ -39,7 +39,7 @@ import torch  # noqa: E402
 
 METRIC = "attention_tflops"
 UNIT = "TFLOP/s"
-LAYERS = {"c1_image512_cpu": 60, "c2_image1024": 60, "c3_image2048": 60, "c4_video480p": 4, "c5_video768p": 1}
+LAYERS = {"c1_image512_cpu": 60, "c2_image1024": 60, "c3_image2048": 20, "c4_video480p": 4, "c5_video768p": 1}
 # DRAM bytes per launch of attn_fwd_kernel on the c2 workload (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the ncu capture summarised in profiles/attn_fwd_kernel_c2_image1024.txt.  None until captured.
 NCU_TRAFFIC_BYTES_C2 = None
@@ -126,18 +126,21 @@ def cpu_attention_sample(cfg, sample_heads: int, min_seconds: float, max_reps: i
     torch.set_num_threads(os.cpu_count() or 1)
     q, k, v, kv_len = make_inputs(cfg, 0, heads=sample_heads)
     q, k, v, kv_len = q[:1], k[:1], v[:1], kv_len[:1]
-    flops = 4.0 * 1 * sample_heads * cfg.seq * cfg.seq * cfg.head_dim
-    attn_oracle.attention_fp32(q[:, :1], k[:, :1], v[:, :1], kv_len=kv_len)  # warm the thread pool
+    # long sequences: a strided sample of query rows against all keys bounds time and memory
+    rows = None if cfg.seq <= 8192 else torch.arange(0, cfg.seq, cfg.seq // 2048)
+    n_rows = cfg.seq if rows is None else len(rows)
+    flops = 4.0 * 1 * sample_heads * n_rows * cfg.seq * cfg.head_dim
+    attn_oracle.attention_fp32(q[:, :1, :256], k[:, :1, :256], v[:, :1, :256])  # warm the thread pool
     times = []
     t_all = time.perf_counter()
     while len(times) < max_reps and (time.perf_counter() - t_all < min_seconds or not times):
         t0 = time.perf_counter()
-        attn_oracle.attention_fp32(q, k, v, kv_len=kv_len)
+        attn_oracle.attention_fp32(q, k, v, kv_len=kv_len, rows=rows)
         times.append(time.perf_counter() - t0)
     best = min(times)
     return {"value": flops / best / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{sample_heads} of {cfg.heads} heads of batch element 0 of one {cfg.name} layer call, "
-                      f"fp32 softmax on CPU, best of {len(times)}"}, times
+            "sample": f"{n_rows} of {cfg.seq} query rows x all keys, {sample_heads} of {cfg.heads} heads of batch "
+                      f"element 0 of one {cfg.name} layer call, fp32 softmax on CPU, best of {len(times)}"}, times
 
 
 def run_reference(args, cfg):
@@ -151,7 +154,8 @@ def run_reference(args, cfg):
         base, times = cpu_attention_sample(cfg, sample_heads, 0.0, 1)
         if i >= args.warmup:
             step_times.append(times[0])
-    flops = 4.0 * sample_heads * cfg.seq * cfg.seq * cfg.head_dim
+    n_rows = cfg.seq if cfg.seq <= 8192 else len(range(0, cfg.seq, cfg.seq // 2048))
+    flops = 4.0 * sample_heads * n_rows * cfg.seq * cfg.head_dim
     total = sum(step_times)
     value = flops * len(step_times) / total / 1e12
     base["value"] = value
@@ -197,6 +201,19 @@ def run_ours(args, cfg):
     my_b = (rank // hg) * b_local
     my_h = (rank % hg) * h_local
 
+    # Ulysses with CFG halves on chip halves: every batch element gets its own sub-group of ranks.
+    group = None
+    cfg_groups = 1
+    if mode == "ulysses" and args.cfg_halves and cfg.batch > 1 and world % cfg.batch == 0 and world > cfg.batch:
+        cfg_groups = cfg.batch
+        for ranks in parallel.cfg_subgroups(world, cfg_groups):
+            g = dist.new_group(ranks)
+            if rank in ranks:
+                group = g
+    sub_world = world // cfg_groups
+    sub_rank = rank % sub_world
+    my_cfg = rank // sub_world
+
     # Resident inputs: one buffer set per layer call.
     sets = []
     for i in range(layers):
@@ -207,7 +224,10 @@ def run_ours(args, cfg):
             v = v[my_b:my_b + b_local, my_h:my_h + h_local].contiguous()
             kv_len = kv_len[my_b:my_b + b_local].contiguous()
         else:
-            q, k, v, kv_len = parallel.make_sequence_shard(cfg, i, rank, world, dev)
+            q, k, v, kv_len = parallel.make_sequence_shard(cfg, i, sub_rank, sub_world, dev)
+            if cfg_groups > 1:   # this half owns one batch element
+                q, k, v = (t[my_cfg:my_cfg + 1].contiguous() for t in (q, k, v))
+                kv_len = kv_len[my_cfg:my_cfg + 1].contiguous()
         sets.append((q, k, v, kv_len, torch.empty_like(q)))
     torch.cuda.synchronize()
 
@@ -219,12 +239,15 @@ def run_ours(args, cfg):
         if mode == "local":
             dtb200.attention(q, k, v, kv_len=kv_len, use_fixed_m=args.fixed_m, mk=mk, out=o)
         elif mode == "ulysses":
-            parallel.ulysses_attention(q, k, v, kv_len=kv_len, out=o)
+            parallel.ulysses_attention(q, k, v, kv_len=kv_len, out=o, group=group)
         else:
             parallel.ring_attention(q, k, v, kv_len=kv_len, out=o)
 
     if args.fixed_m:
         launches_per_call = 4  # two row-norm reductions, the operand kernel, the attention kernel
+    if mode == "ring":
+        launches_per_call = world + 1  # one residual kernel per ring step and the final normalisation
+    launches_per_call *= world         # every rank launches its own
 
     def barrier():
         if world > 1:
@@ -254,6 +277,26 @@ def run_ours(args, cfg):
     dtb200.check_device_status(dev)
 
     # ---- end to end: pinned host buffers -> device -> kernel -> pinned host result, double buffered
+    e2e_ms, e2e_steps, h2d_bytes, d2h_bytes = None, 0, 0, 0
+    if not args.no_e2e:
+        e2e_ms, e2e_steps, h2d_bytes, d2h_bytes = run_e2e(args, mode, layers, sets, world, dev, group, barrier)
+    dtb200.check_device_status(dev)
+
+    if world > 1:
+        t = torch.tensor([ms_total, e2e_ms or 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = t[0].item()
+        e2e_ms = t[1].item() if e2e_ms is not None else None
+    finish(args, cfg, mode, layers, sets, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
+           h2d_bytes, d2h_bytes, launches_per_call, clocks)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, mode, layers, sets, world, dev, group, barrier):
+    import dtb200
+    from dtb200 import parallel
+
     n_host = min(layers, 4)
     host_sets = []
     for i in range(n_host):
@@ -283,7 +326,7 @@ def run_ours(args, cfg):
             if mode == "local":
                 dtb200.attention(dq, dk, dv, kv_len=kv_len, use_fixed_m=args.fixed_m, out=do)
             elif mode == "ulysses":
-                parallel.ulysses_attention(dq, dk, dv, kv_len=kv_len, out=do)
+                parallel.ulysses_attention(dq, dk, dv, kv_len=kv_len, out=do, group=group)
             else:
                 parallel.ring_attention(dq, dk, dv, kv_len=kv_len, out=do)
             out_ready[i % 2].record(compute)
@@ -304,18 +347,15 @@ def run_ours(args, cfg):
         e2e_step()
     f1.record()
     barrier()
-    e2e_ms = f0.elapsed_time(f1)
-    dtb200.check_device_status(dev)
+    return f0.elapsed_time(f1), e2e_steps, h2d_bytes, d2h_bytes
 
-    if world > 1:
-        t = torch.tensor([ms_total, e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, e2e_ms = t.tolist()
 
+def finish(args, cfg, mode, layers, sets, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
+           h2d_bytes, d2h_bytes, launches_per_call, clocks):
     flops_call = cfg.flops()
     flops_step = flops_call * layers
     value = flops_step * args.steps / (ms_total * 1e-3) / 1e12
-    e2e_value = flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    e2e_value = flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12 if e2e_ms else None
     burst, sustained, src = measured_peaks()
     # dominant kernel: attn_fwd_kernel, one launch per layer call per rank; its share of the call's FLOPs
     flops_launch = flops_call / world
@@ -335,7 +375,7 @@ def run_ours(args, cfg):
                 "workload": cfg.name, "B": cfg.batch, "H": cfg.heads, "S": cfg.seq, "D": cfg.head_dim,
                 "layer_calls_per_step": layers, "softmax": "bounded-logit (fixed-m)" if args.fixed_m else "online",
                 "parallelism": {"local": f"cfg{bg}xheads{hg} (resident head-parallel shards, no collective)",
-                                "ulysses": f"ulysses{world} (all-to-all)", "ring": f"ring{world} (KV rotation)"}[mode],
+                                "ulysses": f"cfg{cfg_groups} x ulysses{sub_world} (all-to-all inside each group)", "ring": f"ring{world} (KV rotation)"}[mode],
                 "l2": "inputs larger than L2: every layer call reads its own q/k/v buffers "
                       f"({layers} sets, {3 * sets[0][0].numel() * 2 / 1e6:.0f} MB each per rank)",
                 "inputs": "N(0,1) q,k,v with unit-weight qk-RMSNorm, bf16, trailing text padding 0-300 keys per batch element",
@@ -350,7 +390,8 @@ def run_ours(args, cfg):
                          "peak_source": f"{src} sustained bf16 GEMM (kernel timed inside a long step)",
                          "kernel": "attn_fwd_kernel", "flops_per_launch": flops_launch,
                          "traffic": NCU_TRAFFIC_BYTES_C2 if cfg.name == "c2_image1024" and world == 1 else None},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+            "e2e": None if e2e_ms is None else {
+                    "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
                     "how": "pinned host q,k,v -> device (double buffered, copy streams) -> dtb200.attention -> pinned host o"},
             "gpu_launches": args.steps * layers * launches_per_call,
@@ -358,8 +399,6 @@ def run_ours(args, cfg):
             "cpu_baseline": cpu_base,
         }
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main():
@@ -373,6 +412,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="layer calls per step (default: per workload)")
     ap.add_argument("--fixed-m", action="store_true", help="bounded-logit softmax, operand derived per call")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cfg-halves", action="store_true", help="ulysses: one sub-group of ranks per batch element")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
