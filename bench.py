@@ -233,11 +233,22 @@ def run_ours(args, cfg):
 
     mk = None
     launches_per_call = 1
+    fused = None
+    if mode != "local" and args.transport == "p2p" and sub_world > 1:
+        from dtb200 import symm
+
+        shp = sets[0][0].shape
+        cls = symm.UlyssesP2P if mode == "ulysses" else symm.RingPull
+        fused = cls(shp[0], shp[1], shp[2], group=group, device=dev)
 
     def layer_call(s):
         q, k, v, kv_len, o = s
         if mode == "local":
             dtb200.attention(q, k, v, kv_len=kv_len, use_fixed_m=args.fixed_m, mk=mk, out=o)
+        elif fused is not None and mode == "ulysses":
+            fused(q, k, v, kv_len=kv_len)
+        elif fused is not None:
+            fused(q, k, v, kv_len=kv_len, out=o)
         elif mode == "ulysses":
             parallel.ulysses_attention(q, k, v, kv_len=kv_len, out=o, group=group)
         else:
@@ -279,7 +290,7 @@ def run_ours(args, cfg):
     # ---- end to end: pinned host buffers -> device -> kernel -> pinned host result, double buffered
     e2e_ms, e2e_steps, h2d_bytes, d2h_bytes = None, 0, 0, 0
     if not args.no_e2e:
-        e2e_ms, e2e_steps, h2d_bytes, d2h_bytes = run_e2e(args, mode, layers, sets, world, dev, group, barrier)
+        e2e_ms, e2e_steps, h2d_bytes, d2h_bytes = run_e2e(args, mode, layers, sets, world, dev, group, barrier, fused)
     dtb200.check_device_status(dev)
 
     if world > 1:
@@ -293,7 +304,7 @@ def run_ours(args, cfg):
         dist.destroy_process_group()
 
 
-def run_e2e(args, mode, layers, sets, world, dev, group, barrier):
+def run_e2e(args, mode, layers, sets, world, dev, group, barrier, fused):
     import dtb200
     from dtb200 import parallel
 
@@ -325,6 +336,10 @@ def run_e2e(args, mode, layers, sets, world, dev, group, barrier):
             compute.wait_event(in_ready[i % 2])
             if mode == "local":
                 dtb200.attention(dq, dk, dv, kv_len=kv_len, use_fixed_m=args.fixed_m, out=do)
+            elif fused is not None and mode == "ulysses":
+                do = fused(dq, dk, dv, kv_len=kv_len)
+            elif fused is not None:
+                fused(dq, dk, dv, kv_len=kv_len, out=do)
             elif mode == "ulysses":
                 parallel.ulysses_attention(dq, dk, dv, kv_len=kv_len, out=do, group=group)
             else:
@@ -375,7 +390,8 @@ def finish(args, cfg, mode, layers, sets, world, rank, bg, hg, cfg_groups, sub_w
                 "workload": cfg.name, "B": cfg.batch, "H": cfg.heads, "S": cfg.seq, "D": cfg.head_dim,
                 "layer_calls_per_step": layers, "softmax": "bounded-logit (fixed-m)" if args.fixed_m else "online",
                 "parallelism": {"local": f"cfg{bg}xheads{hg} (resident head-parallel shards, no collective)",
-                                "ulysses": f"cfg{cfg_groups} x ulysses{sub_world} (all-to-all inside each group)", "ring": f"ring{world} (KV rotation)"}[mode],
+                                "ulysses": f"cfg{cfg_groups} x ulysses{sub_world} ({'peer-store exchange fused into the kernels' if args.transport == 'p2p' else 'NCCL all-to-all'})",
+                                "ring": f"ring{world} ({'copy-engine pulls of K/V shards' if args.transport == 'p2p' else 'NCCL send/recv rotation'})"}[mode],
                 "l2": "inputs larger than L2: every layer call reads its own q/k/v buffers "
                       f"({layers} sets, {3 * sets[0][0].numel() * 2 / 1e6:.0f} MB each per rank)",
                 "inputs": "N(0,1) q,k,v with unit-weight qk-RMSNorm, bf16, trailing text padding 0-300 keys per batch element",
@@ -409,6 +425,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_image1024")
     ap.add_argument("--mode", default="auto", choices=["auto", "local", "ulysses", "ring"])
+    ap.add_argument("--transport", default="p2p", choices=["p2p", "nccl"],
+                    help="ulysses/ring: this library's peer-memory kernels (p2p) or NCCL collectives")
     ap.add_argument("--layers", type=int, default=0, help="layer calls per step (default: per workload)")
     ap.add_argument("--fixed-m", action="store_true", help="bounded-logit softmax, operand derived per call")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -102,6 +102,39 @@ __global__ void fixed_m_finish_kernel(const float* __restrict__ norms, int Hq, i
 }
 
 // ---------------------------------------------------------------------------
+// Sequence shards -> head shards without an intermediate copy: rank `rank` holds x[B, H, Sl, D] (all
+// heads of its sequence shard) and writes head group r of it straight into rank r's buffer
+// y_r[B, H/P, P*Sl, D] at rows [rank*Sl, (rank+1)*Sl), 16 bytes per thread, 256-byte rows coalesced.
+// Destinations may be peer memory (plain stores over NVLink).  grid.y selects one of up to 3 tensors.
+// ---------------------------------------------------------------------------
+struct ScatterHeadsParams {
+  const __nv_bfloat16* src[3];
+  int64_t sb[3], sh[3], ss[3];
+  __nv_bfloat16* dst[3][8];
+  int B, H, Sl, P, rank;
+};
+
+__global__ void __launch_bounds__(256) scatter_heads_kernel(const __grid_constant__ ScatterHeadsParams sp) {
+  const int which = blockIdx.y;
+  const int Hl = sp.H / sp.P;
+  const int64_t chunks = static_cast<int64_t>(sp.B) * sp.H * sp.Sl * 16;   // 16-byte chunks
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < chunks;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(idx & 15);
+    const int64_t rowid = idx >> 4;
+    const int sl = static_cast<int>(rowid % sp.Sl);
+    const int h = static_cast<int>((rowid / sp.Sl) % sp.H);
+    const int b = static_cast<int>(rowid / (static_cast<int64_t>(sp.Sl) * sp.H));
+    const uint4 v = reinterpret_cast<const uint4*>(sp.src[which] + b * sp.sb[which] + h * sp.sh[which] + sl * sp.ss[which])[c];
+    const int r = h / Hl;
+    __nv_bfloat16* drow = sp.dst[which][r] +
+                          ((static_cast<int64_t>(b) * Hl + (h - r * Hl)) * (static_cast<int64_t>(sp.P) * sp.Sl) +
+                           static_cast<int64_t>(sp.rank) * sp.Sl + sl) * kHeadDim;
+    reinterpret_cast<uint4*>(drow)[c] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------
 int check_params(const dtb_attn_params* p, bool need_o) {
   if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr) return DTB_ERR_NULL;
   if (need_o && p->o == nullptr) return DTB_ERR_NULL;
@@ -189,6 +222,10 @@ int fill_kernel_params(const dtb_attn_params* p, AttnKernelParams* kp) {
   kp->zero_padded_rows = (p->flags & DTB_FLAG_ZERO_PADDED_ROWS) ? 1 : 0;
   const float scale = p->scale > 0.f ? p->scale : 1.0f / sqrtf(static_cast<float>(p->D));
   kp->scale_log2 = scale * kLog2e;
+  for (int i = 0; i < 8; ++i) kp->o_peer[i] = nullptr;
+  kp->o_shard_rows = 0;
+  kp->o_total_heads = 0;
+  kp->o_head_offset = 0;
   return DTB_OK;
 }
 
@@ -396,3 +433,62 @@ extern "C" int dtb_debug_read_wait_profile(unsigned long long* out) {
   return DTB_OK;
 }
 #endif
+
+extern "C" int dtb_attn_fwd_scatter(const dtb_attn_params* p, const dtb_attn_scatter* sc, void* stream) {
+  int st = check_params(p, false);
+  if (st != DTB_OK) return st;
+  if (sc == nullptr) return DTB_ERR_NULL;
+  if (sc->n_peers < 1 || sc->n_peers > 8 || sc->shard_rows <= 0 || sc->total_heads < p->Hq || sc->head_offset < 0 ||
+      sc->head_offset + p->Hq > sc->total_heads)
+    return DTB_ERR_SHAPE;
+  if (static_cast<int64_t>(sc->shard_rows) * sc->n_peers < p->Sq) return DTB_ERR_SHAPE;
+  for (int i = 0; i < sc->n_peers; ++i) {
+    if (sc->out_ptrs[i] == nullptr) return DTB_ERR_NULL;
+    if (reinterpret_cast<uintptr_t>(sc->out_ptrs[i]) & 15u) return DTB_ERR_ALIGN;
+  }
+  if (!device_is_sm100()) return DTB_ERR_ARCH;
+  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
+  AttnKernelParams kp;
+  st = fill_kernel_params(p, &kp);
+  if (st != DTB_OK) return st;
+  for (int i = 0; i < sc->n_peers; ++i) kp.o_peer[i] = static_cast<__nv_bfloat16*>(sc->out_ptrs[i]);
+  kp.o_shard_rows = sc->shard_rows;
+  kp.o_total_heads = sc->total_heads;
+  kp.o_head_offset = sc->head_offset;
+  attn_fwd_kernel<false><<<dim3(q_blocks(p), p->Hq, p->B), dim3(kNumThreads), kSmemBytes,
+                           static_cast<cudaStream_t>(stream)>>>(kp);
+  return launch_ok("attn_fwd_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
+}
+
+extern "C" int dtb_scatter_heads(const dtb_scatter_heads_params* sp, void* stream) {
+  if (sp == nullptr) return DTB_ERR_NULL;
+  if (sp->n_tensors < 1 || sp->n_tensors > 3 || sp->n_peers < 1 || sp->n_peers > 8) return DTB_ERR_SHAPE;
+  if (sp->B <= 0 || sp->H <= 0 || sp->S_local <= 0 || sp->D != kHeadDim || sp->H % sp->n_peers != 0 || sp->rank < 0 ||
+      sp->rank >= sp->n_peers)
+    return DTB_ERR_SHAPE;
+  ScatterHeadsParams kp;
+  for (int t = 0; t < 3; ++t) {
+    const int u = t < sp->n_tensors ? t : 0;
+    if (sp->src[u] == nullptr) return DTB_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(sp->src[u]) & 15u) || (sp->stride_b[u] & 7) || (sp->stride_h[u] & 7) || (sp->stride_s[u] & 7))
+      return DTB_ERR_ALIGN;
+    kp.src[t] = static_cast<const __nv_bfloat16*>(sp->src[u]);
+    kp.sb[t] = sp->stride_b[u];
+    kp.sh[t] = sp->stride_h[u];
+    kp.ss[t] = sp->stride_s[u];
+    for (int r = 0; r < 8; ++r) {
+      void* d = r < sp->n_peers ? sp->dst[u][r] : nullptr;
+      if (r < sp->n_peers && (d == nullptr || (reinterpret_cast<uintptr_t>(d) & 15u))) return d ? DTB_ERR_ALIGN : DTB_ERR_NULL;
+      kp.dst[t][r] = static_cast<__nv_bfloat16*>(d);
+    }
+  }
+  kp.B = sp->B;
+  kp.H = sp->H;
+  kp.Sl = sp->S_local;
+  kp.P = sp->n_peers;
+  kp.rank = sp->rank;
+  const int64_t chunks = static_cast<int64_t>(sp->B) * sp->H * sp->S_local * 16;
+  const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((chunks + 255) / 256, 148 * 8));
+  scatter_heads_kernel<<<dim3(blocks, sp->n_tensors), 256, 0, static_cast<cudaStream_t>(stream)>>>(kp);
+  return launch_ok("scatter_heads_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
+}

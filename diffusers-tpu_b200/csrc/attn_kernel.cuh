@@ -110,6 +110,11 @@ struct AttnKernelParams {
   int acc_init;               // residual mode: start from the empty state
   int zero_padded_rows;
   float scale_log2;           // softmax scale * log2(e)
+  // Head-parallel call with a sequence-sharded output (o_shard_rows > 0): query row s of local head h
+  // goes to o_peer[s / o_shard_rows], a contiguous [B, o_total_heads, o_shard_rows, D] buffer that may
+  // live on another GPU (plain peer stores), at head o_head_offset + h and row s % o_shard_rows.
+  __nv_bfloat16* o_peer[8];
+  int o_shard_rows, o_total_heads, o_head_offset;
 };
 
 // Warp-uniform bounded wait: every lane polls, and the warp agrees on the outcome so
@@ -257,7 +262,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       const int row = q0 + threadIdx.x;
       if (row < p.Sq) {
         if (!kResidual) {
-          uint4* dst = reinterpret_cast<uint4*>(p.o + b * p.o_stride_b + h * p.o_stride_h + row * p.o_stride_s);
+          uint4* dst;
+          if (p.o_shard_rows > 0) {
+            const int dest = row / p.o_shard_rows;
+            dst = reinterpret_cast<uint4*>(
+                p.o_peer[dest] + ((static_cast<int64_t>(b) * p.o_total_heads + p.o_head_offset + h) * p.o_shard_rows +
+                                  (row - dest * p.o_shard_rows)) * kHeadDim);
+          } else {
+            dst = reinterpret_cast<uint4*>(p.o + b * p.o_stride_b + h * p.o_stride_h + row * p.o_stride_s);
+          }
 #pragma unroll
           for (int i = 0; i < kHeadDim * 2 / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
         } else if (p.acc_init) {
@@ -550,23 +563,48 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
           p.acc_l[acc_row] = l_sum;
         }
       } else {
+        // Normalise, round to bf16 and stage the 32 rows of this warp in the (now dead) Q tile of
+        // this group, 16-byte chunks XOR-swizzled by row so neither side bank-conflicts; then the warp
+        // writes whole 256-byte rows, two per store instruction, to this GPU's output or, for a
+        // head-parallel call whose output is sequence-sharded, straight into the owning peer's buffer.
         const bool padded = p.zero_padded_rows && (p.q_offset + row >= kv_len_b);
         const float inv = (l_sum > 0.f && !padded) ? (1.0f / l_sum) : 0.f;
-        uint4* dst = reinterpret_cast<uint4*>(p.o + b * p.o_stride_b + h * p.o_stride_h + row * p.o_stride_s);
+        uint8_t* stage = smem_q + t * kTileBytes + (warp & 3) * (32 * kHeadDim * 2);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           tmem_ld32_sync(o_tmem + c * 32, r);
-          if (row_in_range) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
-              v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
-              v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
-              v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
-              dst[c * 4 + i] = v;
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+            const int chunk = c * 4 + i;
+            *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = v;
+          }
+        }
+        __syncwarp();
+        const int row0 = q0 + t * kBlockM + (warp & 3) * 32;   // first query row of this warp
+        const int sub = lane >> 4;                              // which of the two rows of a store
+        const int chunk = lane & 15;
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+          const int rl = 2 * i + sub;
+          const int grow = row0 + rl;
+          if (grow < p.Sq) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + rl * 256 + ((chunk ^ (rl & 15)) << 4));
+            __nv_bfloat16* dst_row;
+            if (p.o_shard_rows > 0) {
+              const int dest = grow / p.o_shard_rows;
+              dst_row = p.o_peer[dest] +
+                        ((static_cast<int64_t>(b) * p.o_total_heads + p.o_head_offset + h) * p.o_shard_rows +
+                         (grow - dest * p.o_shard_rows)) * kHeadDim;
+            } else {
+              dst_row = p.o + b * p.o_stride_b + h * p.o_stride_h + grow * p.o_stride_s;
             }
+            reinterpret_cast<uint4*>(dst_row)[chunk] = v;
           }
         }
       }

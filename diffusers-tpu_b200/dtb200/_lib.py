@@ -25,7 +25,8 @@ STATIC_SCRATCH_BYTES = 32 << 20
 # Every symbol the public header declares; tests check that the library exports all of them.
 EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
-    "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands",
+    "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_scatter_heads",
+    "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands",
     "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_mma_rate",
 )
 
@@ -53,6 +54,27 @@ class AttnResidual(ctypes.Structure):
     _fields_ = [
         ("o_acc", ctypes.c_void_p), ("m", ctypes.c_void_p), ("l", ctypes.c_void_p),
         ("kv_offset", ctypes.c_int32), ("q_offset", ctypes.c_int32), ("init", ctypes.c_int32),
+    ]
+
+
+class AttnScatter(ctypes.Structure):
+    """Mirror of ``dtb_attn_scatter``."""
+
+    _fields_ = [
+        ("out_ptrs", ctypes.c_void_p * 8), ("n_peers", ctypes.c_int32), ("shard_rows", ctypes.c_int32),
+        ("head_offset", ctypes.c_int32), ("total_heads", ctypes.c_int32),
+    ]
+
+
+class ScatterHeadsParams(ctypes.Structure):
+    """Mirror of ``dtb_scatter_heads_params``."""
+
+    _fields_ = [
+        ("src", ctypes.c_void_p * 3),
+        ("stride_b", ctypes.c_int64 * 3), ("stride_h", ctypes.c_int64 * 3), ("stride_s", ctypes.c_int64 * 3),
+        ("dst", (ctypes.c_void_p * 8) * 3),
+        ("n_tensors", ctypes.c_int32), ("n_peers", ctypes.c_int32), ("rank", ctypes.c_int32),
+        ("B", ctypes.c_int32), ("H", ctypes.c_int32), ("S_local", ctypes.c_int32), ("D", ctypes.c_int32),
     ]
 
 
@@ -89,6 +111,10 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         lib.dtb_attn_fwd.argtypes = [ctypes.POINTER(AttnParams), vp, ctypes.c_size_t, vp]
         lib.dtb_attn_fwd_static_scratch.restype = ctypes.c_int
         lib.dtb_attn_fwd_static_scratch.argtypes = [ctypes.POINTER(AttnParams), vp]
+        lib.dtb_attn_fwd_scatter.restype = ctypes.c_int
+        lib.dtb_attn_fwd_scatter.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnScatter), vp]
+        lib.dtb_scatter_heads.restype = ctypes.c_int
+        lib.dtb_scatter_heads.argtypes = [ctypes.POINTER(ScatterHeadsParams), vp]
         lib.dtb_attn_fwd_residual.restype = ctypes.c_int
         lib.dtb_attn_fwd_residual.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnResidual), vp]
         lib.dtb_attn_finalize.restype = ctypes.c_int

@@ -72,6 +72,28 @@ typedef struct dtb_attn_residual {
   int32_t init;      /* non-zero: start from the empty state instead of reading o_acc / m / l */
 } dtb_attn_residual;
 
+/* Destination of a head-parallel call whose output is sequence-sharded over `n_peers` GPUs: query row s of
+ * local head h is written to out_ptrs[s / shard_rows], a contiguous bf16 [B, total_heads, shard_rows, D]
+ * buffer (possibly another GPU's memory, mapped into this process), at head head_offset + h. */
+typedef struct dtb_attn_scatter {
+  void* out_ptrs[8];
+  int32_t n_peers;
+  int32_t shard_rows;
+  int32_t head_offset;
+  int32_t total_heads;
+} dtb_attn_scatter;
+
+/* Sequence shards -> head shards for up to three tensors at once (q, k, v): this rank's bf16
+ * [B, H, S_local, D] tensors (element strides given) are written straight into every rank's contiguous
+ * [B, H / n_peers, n_peers * S_local, D] buffers dst[tensor][peer], rows [rank * S_local, (rank+1) * S_local). */
+typedef struct dtb_scatter_heads_params {
+  const void* src[3];
+  int64_t stride_b[3], stride_h[3], stride_s[3];
+  void* dst[3][8];
+  int32_t n_tensors, n_peers, rank;
+  int32_t B, H, S_local, D;
+} dtb_scatter_heads_params;
+
 /* Library version and a human-readable string for a status code. */
 int dtb_version(void);
 const char* dtb_status_string(int status);
@@ -89,6 +111,18 @@ size_t dtb_attn_workspace_bytes(const dtb_attn_params* p);
  * Replaces diffusers_tpu/kernels/splash.py:566-650 `attention(...)` (and the per-sample loop around it
  * in diffusers_tpu/models/moss_image/jax_dit.py:199-203: kv_len is per batch element here). */
 int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* dtb_attn_fwd for a head shard [B, H/P, S, D] whose output goes back to sequence shards: the epilogue stores each
+ * output row directly into the buffer of the rank that owns it (peer stores over NVLink), which fuses the
+ * heads -> sequence all-to-all of diffusers_tpu/backends/qwen21_core_tt.py:116-121 (and the output sharding
+ * constraint of diffusers_tpu/kernels/mesh_attention.py:118-120, 145) into the kernel.  p->o is ignored.
+ * The caller synchronises the ranks before the buffers are read. */
+int dtb_attn_fwd_scatter(const dtb_attn_params* p, const dtb_attn_scatter* sc, void* stream);
+
+/* The sequence -> heads exchange of q, k and v as one kernel of peer stores; replaces the first all-to-all of
+ * diffusers_tpu/backends/qwen21_core_tt.py:108-115 (`_a2a` to heads).  The caller synchronises the ranks before
+ * the destination buffers are read. */
+int dtb_scatter_heads(const dtb_scatter_heads_params* sp, void* stream);
 
 /* Residual forward over one KV shard: folds this shard into the running (o_acc, m, l) state.
  * Replaces diffusers_tpu/kernels/splash.py:665-742 `residual_attention(...)` together with the

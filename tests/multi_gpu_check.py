@@ -1,6 +1,6 @@
 """Run under torchrun on N GPUs: checks a multi-GPU driver against the CPU oracle on sampled rows.
 
-    python -m torch.distributed.run --nproc-per-node N tests/multi_gpu_check.py {ulysses|ring} [S] [H] [B]
+    python -m torch.distributed.run --nproc-per-node N tests/multi_gpu_check.py {ulysses|ring|ulysses-p2p|ring-pull} [S] [H] [B]
 """
 import os
 import sys
@@ -35,8 +35,16 @@ def main():
     Sl = S // world
     sl = slice(rank * Sl, (rank + 1) * Sl)
     shard = [t[:, :, sl].contiguous().to(dev) for t in (q, k, v)]
-    fn = parallel.ulysses_attention if mode == "ulysses" else parallel.ring_attention
-    out = fn(*shard, kv_len=kv_len.to(dev))
+    if mode in ("ulysses", "ring"):
+        fn = parallel.ulysses_attention if mode == "ulysses" else parallel.ring_attention
+        out = fn(*shard, kv_len=kv_len.to(dev))
+    else:
+        from dtb200 import symm
+
+        cls = symm.UlyssesP2P if mode == "ulysses-p2p" else symm.RingPull
+        op = cls(B, H, Sl, device=dev)
+        for _ in range(2):      # twice: buffers are reused across calls
+            out = op(*shard, kv_len=kv_len.to(dev)).clone()
     dtb200.check_device_status(dev)
     rows = torch.arange(rank * Sl, (rank + 1) * Sl, max(1, Sl // 64))
     ref = O.attention_fp32(q, k, v, kv_len=kv_len, rows=rows)

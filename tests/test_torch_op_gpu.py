@@ -45,7 +45,7 @@ def test_dispatch_hook_layout_and_fallback_rules():
         torch_op.dispatch(*bshd, is_causal=True)
 
 
-@pytest.mark.parametrize("mode", ["ulysses", "ring"])
+@pytest.mark.parametrize("mode", ["ulysses", "ring", "ulysses-p2p", "ring-pull"])
 def test_two_gpu_drivers(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -55,3 +55,48 @@ def test_two_gpu_drivers(mode):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "PARITY OK" in r.stdout
+
+
+def test_scatter_entry_points_with_local_buffers_as_peers():
+    """One GPU stands in for four ranks: the `peer` buffers are ordinary local tensors."""
+    import ctypes
+
+    from dtb200 import _lib, ops
+
+    P, B, H, Sl = 4, 2, 8, 160
+    Hl, S = H // P, P * Sl
+    q, k, v = _rand(B, H, S, 3)
+    dev = torch.device("cuda")
+    full = [t.to(dev) for t in (q, k, v)]
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    # sequence shards -> head shards, rank by rank
+    y = [[torch.zeros(B, Hl, S, 128, dtype=torch.bfloat16, device=dev) for _ in range(P)] for _ in range(3)]
+    for rank in range(P):
+        sp = _lib.ScatterHeadsParams()
+        shards = [t[:, :, rank * Sl:(rank + 1) * Sl] for t in full]        # strided views, addressed in place
+        for i, t in enumerate(shards):
+            sp.src[i] = t.data_ptr()
+            sp.stride_b[i], sp.stride_h[i], sp.stride_s[i] = t.stride()[:3]
+            for r in range(P):
+                sp.dst[i][r] = y[i][r].data_ptr()
+        sp.n_tensors, sp.n_peers, sp.rank, sp.B, sp.H, sp.S_local, sp.D = 3, P, rank, B, H, Sl, 128
+        _lib.check(lib.dtb_scatter_heads(ctypes.byref(sp), stream), "dtb_scatter_heads")
+    for i in range(3):
+        for r in range(P):
+            assert torch.equal(y[i][r], full[i][:, r * Hl:(r + 1) * Hl])
+    # attention on each head shard with the output scattered back to sequence shards
+    kv_len = torch.tensor([S, S - 100], dtype=torch.int32, device=dev)
+    outs = [torch.full((B, H, Sl, 128), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(P)]
+    for rank in range(P):
+        p = ops._fill_params(y[0][rank], y[1][rank], y[2][rank], None, kv_len, None, None, _lib.FLAG_ZERO_PADDED_ROWS, 1,
+                             ops._status_buffer(dev))
+        sc = _lib.AttnScatter()
+        for r in range(P):
+            sc.out_ptrs[r] = outs[r].data_ptr()
+        sc.n_peers, sc.shard_rows, sc.head_offset, sc.total_heads = P, Sl, rank * Hl, H
+        _lib.check(lib.dtb_attn_fwd_scatter(ctypes.byref(p), ctypes.byref(sc), stream), "dtb_attn_fwd_scatter")
+    dtb200.check_device_status(dev)
+    got = torch.cat(outs, dim=2)
+    want = dtb200.attention(*full, kv_len=kv_len)
+    assert torch.equal(got, want)
