@@ -102,7 +102,8 @@ __device__ __forceinline__ void report_error(const AbortCtx& ctx, int code, int 
 }
 
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int site) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int site,
+                                          uint64_t budget_ns = kWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
@@ -110,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3f) == 0) {
       if (*ctx.cta_abort) return false;
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (globaltimer_ns() - t0 > budget_ns) {
         report_error(ctx, DEV_ERR_WAIT_TIMEOUT, site, static_cast<int>(parity));
         return false;
       }

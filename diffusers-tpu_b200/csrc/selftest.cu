@@ -234,6 +234,24 @@ __global__ void __launch_bounds__(128) mma_rate_kernel(int mode, int iters, long
   if (warp == 0) tmem_dealloc(tbase, 512);
 }
 
+// Bounded-wait probe: waits on an mbarrier that nothing will ever arrive on.  The wait must give up
+// after `budget_ns`, record DEV_ERR_WAIT_TIMEOUT with the site id in the status words and return, leaving
+// the context usable.
+__global__ void __launch_bounds__(32) wait_timeout_kernel(unsigned long long budget_ns, int site, int* status,
+                                                          int* returned) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  AbortCtx ctx{&abort_flag, status};
+  const bool ok = mbar_wait(smem_u32(&bar), 0, ctx, site, budget_ns);
+  if (threadIdx.x == 0) *returned = ok ? 1 : 2;
+}
+
 int launch_tile_test(int mode, const void* a, const void* b, float* out, int32_t* status, void* stream) {
   if (a == nullptr || b == nullptr || out == nullptr) return DTB_ERR_NULL;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
@@ -285,4 +303,12 @@ extern "C" int dtb_selftest_mma_rate(int mode, int iters, long long* out_cycles,
     return DTB_ERR_LAUNCH;
   dtb::mma_rate_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(mode, iters, out_cycles, status);
   return dtb::launch_ok("mma_rate_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
+}
+
+extern "C" int dtb_selftest_wait_timeout(unsigned long long budget_ns, int site, int32_t* status, int32_t* returned,
+                                         void* stream) {
+  if (status == nullptr || returned == nullptr) return DTB_ERR_NULL;
+  if (budget_ns == 0 || budget_ns > 2000000000ull) return DTB_ERR_SHAPE;
+  dtb::wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(budget_ns, site, status, returned);
+  return dtb::launch_ok("wait_timeout_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }

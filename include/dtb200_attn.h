@@ -159,6 +159,9 @@ int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* stream);
 int dtb_selftest_tmem_roundtrip(const float* in, float* out, int32_t* status, void* stream);
 int dtb_selftest_qk(const void* q, const void* k, float* s_out, int32_t* status, void* stream);
 int dtb_selftest_pv(const void* p, const void* v, float* o_out, int32_t* status, void* stream);
+/* Bounded-wait probe: one warp waits on a barrier that is never signalled; after budget_ns (<= 2 s) the wait gives up,
+ * writes {1 (timeout), site, CTA, parity} to `status` (4 x int32, zeroed by the caller) and 2 to *returned. */
+int dtb_selftest_wait_timeout(unsigned long long budget_ns, int site, int32_t* status, int32_t* returned, void* stream);
 /* Tensor-pipe rate probe on one SM: `iters` rounds of eight back-to-back 16-deep MMAs.  mode 0: both operands
  * in shared memory, N = 128; 1: N = 64; 2: A operand in tensor memory, N = 128; 3: N = 256.
  * out_cycles (device, 3 x int64): cycles spent issuing, cycles until completion, 1 if completed. */

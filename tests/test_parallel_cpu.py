@@ -124,3 +124,37 @@ def test_placement_and_schedule():
             assert sched[0] == rank and sorted(sched) == list(range(world))
     # what rank r holds at step t is what rank r-1 held at step t-1
     assert parallel.ring_schedule(3, 8)[2] == parallel.ring_schedule(2, 8)[1]
+
+
+def _absent_peer_worker(rank, world, port, result_dir):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    q, _, _ = _inputs(1, 2, 64, seed=1)
+    if rank == 1:
+        # this rank leaves between steps, before the exchange: nothing of its is in flight
+        open(os.path.join(result_dir, "left_1"), "w").close()
+        os._exit(0)
+    try:
+        parallel.seq_to_heads(q[:, :, :32].contiguous())
+        outcome = "completed"
+    except Exception as e:  # the exchange must end with an error, not hang
+        outcome = "error:" + type(e).__name__
+    open(os.path.join(result_dir, "rank0_" + outcome.split(":")[0]), "w").close()
+    os._exit(0)
+
+
+def test_exchange_with_an_absent_peer_errors_instead_of_hanging(tmp_path):
+    """Host-side failure detection: a rank that leaves before a collective makes its peer's call fail within the
+    process-group timeout.  CPU ranks only; no GPU work is involved."""
+    import time
+
+    t0 = time.time()
+    ctx = mp.spawn(_absent_peer_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=False)
+    deadline = t0 + 90
+    while not ctx.join(timeout=1):
+        assert time.time() < deadline, "ranks did not finish: the exchange hung"
+    names = sorted(os.listdir(tmp_path))
+    assert "left_1" in names and "rank0_error" in names, names

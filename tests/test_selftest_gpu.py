@@ -37,3 +37,37 @@ def test_pv_tile_matches_matmul_with_asymmetric_data():
     o = torch.zeros(128, 128, device="cuda")
     _run(_lib.load().dtb_selftest_pv, p, v, o)
     torch.testing.assert_close(o, p.float() @ v.float(), rtol=1e-5, atol=1e-4)
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A wait nothing will satisfy must end by itself, report where it gave up and leave the GPU usable."""
+    import time
+
+    lib = _lib.load()
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    returned = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0 = time.perf_counter()
+    _lib.check(lib.dtb_selftest_wait_timeout(50_000_000, 77, status.data_ptr(), returned.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream), "dtb_selftest_wait_timeout")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    assert returned.item() == 2
+    st = status.tolist()
+    assert st[0] == 1 and st[1] == 77 and st[2] == 0
+    # the context is intact: ordinary work still runs
+    x = torch.randn(128, 128, device="cuda")
+    y = torch.zeros_like(x)
+    _run(lib.dtb_selftest_tmem_roundtrip, x, y)
+    assert torch.equal(x, y)
+
+
+def test_mma_rate_probe_completes():
+    lib = _lib.load()
+    out = torch.zeros(3, dtype=torch.int64, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for mode in range(4):
+        _lib.check(lib.dtb_selftest_mma_rate(mode, 100, out.data_ptr(), status.data_ptr(), None), "dtb_selftest_mma_rate")
+        torch.cuda.synchronize()
+        issue, total, ok = out.tolist()
+        assert ok == 1 and 0 < total < 100 * 8 * 400      # well under 400 cycles per 16-deep MMA
+    assert status.tolist() == [0, 0, 0, 0]
