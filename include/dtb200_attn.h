@@ -39,7 +39,6 @@ enum dtb_status {
 /* Flags for dtb_attn_params.flags */
 #define DTB_FLAG_ZERO_PADDED_ROWS 0x1u /* write exact zeros to query rows >= kv_len[b]            */
 #define DTB_FLAG_BOUNDED_LOGITS 0x2u   /* per-head constant softmax offset from `mk` (fixed-m)    */
-#define DTB_FLAG_SIMPLE_KERNEL 0x4u    /* force the single-tile validation kernel                 */
 
 /* One attention call.  All pointers are device pointers unless noted. */
 typedef struct dtb_attn_params {
