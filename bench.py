@@ -417,6 +417,49 @@ def finish(args, cfg, mode, layers, sets, world, rank, bg, hg, cfg_groups, sub_w
         print(json.dumps(line))
 
 
+def run_prepass(args, cfg):
+    """HBM-bound pre-pass (q/k RMSNorm + rotary + layout) on the workload's shapes: GB/s against the copy peak."""
+    import dtb200
+
+    dev = torch.device("cuda", 0)
+    B, S, H = cfg.batch, cfg.seq, cfg.heads
+    n_sets = max(2, min(8, int(2e9 // (6 * B * S * H * 256))))      # rotate buffer sets larger than L2
+    g = torch.Generator(device="cuda").manual_seed(0)
+    sets = [tuple(torch.randn(B, S, H, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+                  for _ in range(3)) for _ in range(n_sets)]
+    ang = torch.arange(S, device=dev, dtype=torch.float32)[:, None] * torch.linspace(1e-4, 1.0, 48, device=dev)[None, :]
+    rope = (torch.cat([ang.cos()] * 2, -1), torch.cat([ang.sin()] * 2, -1))
+    w = torch.ones(128, device=dev)
+    kv_len = torch.full((B,), S - 100, dtype=torch.int32, device=dev)
+    call = lambda i: dtb200.qk_prepass(*sets[i % n_sets], q_weight=w, k_weight=w, rope=rope, kv_len=kv_len, want_mk=True)
+    for i in range(max(args.warmup, 3) * n_sets):
+        call(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = args.steps * n_sets
+    e0.record()
+    for i in range(n):
+        call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    algo_bytes = 3 * 2 * B * S * H * 256
+    hbm = 6549.1
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        hbm = float(json.load(open(path))["hbm_gbs"])
+    gbs = algo_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "qk_prepass_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms * n_sets, "ms_per_call": ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg.name + " pre-pass", "B": B, "S": S, "H": H, "D": 128, "rotary": 96,
+                   "l2": f"{n_sets} rotating buffer sets of {algo_bytes / 2e6:.0f} MB inputs"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                     "algorithmic_bytes_per_launch": algo_bytes, "kernel": "qk_prepass_kernel", "traffic": None},
+        "gpu_launches": 2 * n,
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -432,6 +475,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cfg-halves", action="store_true", help="ulysses: one sub-group of ranks per batch element")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--kernel", default="attention", choices=["attention", "prepass"],
+                    help="attention (the metric's kernel) or the HBM-bound q/k pre-pass in front of it")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -440,6 +485,8 @@ def main():
     cfg = CONFIGS[args.workload]
     if args.impl == "reference":
         run_reference(args, cfg)
+    elif args.kernel == "prepass":
+        run_prepass(args, cfg)
     else:
         run_ours(args, cfg)
 

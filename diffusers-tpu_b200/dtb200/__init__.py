@@ -12,6 +12,7 @@ from .ops import (  # noqa: F401
     check_device_status,
     finalize_residual,
     fixed_m_operands,
+    qk_prepass,
     residual_attention,
     residual_attention_,
     sdpa,
@@ -19,5 +20,5 @@ from .ops import (  # noqa: F401
 
 __all__ = [
     "attention", "residual_attention", "residual_attention_", "finalize_residual", "fixed_m_operands",
-    "sdpa", "ResidualState", "check_device_status", "FIXED_M_SAFE_BOUND", "FIXED_M_RING_SAFE_BOUND",
+    "sdpa", "qk_prepass", "ResidualState", "check_device_status", "FIXED_M_SAFE_BOUND", "FIXED_M_RING_SAFE_BOUND",
 ]

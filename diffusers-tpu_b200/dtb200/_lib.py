@@ -26,7 +26,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
     "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_scatter_heads",
-    "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands",
+    "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands", "dtb_qk_prepass",
     "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_mma_rate", "dtb_selftest_wait_timeout",
 )
 
@@ -78,6 +78,22 @@ class ScatterHeadsParams(ctypes.Structure):
     ]
 
 
+class PrepassParams(ctypes.Structure):
+    """Mirror of ``dtb_prepass_params``."""
+
+    _fields_ = [
+        ("q_in", ctypes.c_void_p), ("k_in", ctypes.c_void_p), ("v_in", ctypes.c_void_p),
+        ("q_strides", ctypes.c_int64 * 3), ("k_strides", ctypes.c_int64 * 3), ("v_strides", ctypes.c_int64 * 3),
+        ("q_out", ctypes.c_void_p), ("k_out", ctypes.c_void_p), ("v_out", ctypes.c_void_p),
+        ("q_weight", ctypes.c_void_p), ("k_weight", ctypes.c_void_p),
+        ("cos", ctypes.c_void_p), ("sin", ctypes.c_void_p), ("kv_len", ctypes.c_void_p),
+        ("norms", ctypes.c_void_p), ("mk_out", ctypes.c_void_p),
+        ("eps", ctypes.c_float), ("scale", ctypes.c_float), ("gate", ctypes.c_float),
+        ("B", ctypes.c_int32), ("S", ctypes.c_int32), ("H", ctypes.c_int32), ("D", ctypes.c_int32),
+        ("rotary", ctypes.c_int32),
+    ]
+
+
 _lock = threading.Lock()
 _lib = None
 
@@ -111,6 +127,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         lib.dtb_attn_fwd.argtypes = [ctypes.POINTER(AttnParams), vp, ctypes.c_size_t, vp]
         lib.dtb_attn_fwd_static_scratch.restype = ctypes.c_int
         lib.dtb_attn_fwd_static_scratch.argtypes = [ctypes.POINTER(AttnParams), vp]
+        lib.dtb_qk_prepass.restype = ctypes.c_int
+        lib.dtb_qk_prepass.argtypes = [ctypes.POINTER(PrepassParams), vp]
         lib.dtb_attn_fwd_scatter.restype = ctypes.c_int
         lib.dtb_attn_fwd_scatter.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(AttnScatter), vp]
         lib.dtb_scatter_heads.restype = ctypes.c_int

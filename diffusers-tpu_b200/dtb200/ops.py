@@ -323,3 +323,77 @@ def sdpa(
     """SDPA-signature callable, ``[B, H, S, D]`` in and out (``mesh_attention.py:218-228``)."""
     del attn_mask, dropout_p, is_causal, enable_gqa  # Not supported, as in the reference.
     return attention(query, key, value, scale=scale, kv_len=kv_len, use_fixed_m=use_fixed_m)
+
+
+def qk_prepass(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: Optional[torch.Tensor] = None,
+    *,
+    q_weight: Optional[torch.Tensor] = None,
+    k_weight: Optional[torch.Tensor] = None,
+    eps: float = 1e-5,
+    rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+    kv_len: KvLen = None,
+    scale: Optional[float] = None,
+    want_mk: bool = False,
+    gate: float = FIXED_M_SAFE_BOUND,
+):
+    """Fused per-head RMSNorm + rotary embedding + pad zeroing + ``(B, S, H, D) -> (B, H, S, D)``.
+
+    ``query, key, value`` are the projections as a DiT block produces them, ``(B, seq, heads, 128)`` bf16
+    (any strides with a contiguous last axis); ``rope = (cos, sin)`` are ``(seq, rotary)`` tables that rotate
+    the leading ``rotary`` channels and pass the rest through (``apply_rope``,
+    ``diffusers_tpu/models/minimax_h3/jax_dit.py:251-262``); the norm is ``x * rsqrt(mean(x^2) + eps) * weight``
+    in f32 (``:191-195``); rows at or past ``kv_len[b]`` come out as zeros (``:372-381``).  Returns
+    ``(q, k, v, mk)`` laid out ``(B, H, S, D)``; ``mk`` is the ``(2, H)`` bounded-logit operand of the returned
+    q and k (``diffusers_tpu/kernels/fixed_m_bound.py:98-118``) when ``want_mk``, else ``None``.
+    """
+    tensors = [query, key] + ([value] if value is not None else [])
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("qk_prepass needs CUDA tensors: dtb200 has no CPU path")
+        if t.dtype != torch.bfloat16 or t.dim() != 4 or t.shape[-1] != 128:
+            raise NotImplementedError(f"expected bf16 (B, S, H, 128), got {t.dtype} {tuple(t.shape)}")
+        if t.shape != query.shape:
+            raise ValueError("query, key and value must have the same shape")
+    tensors = [t if (t.stride(-1) == 1 and all(s % 4 == 0 for s in t.stride()[:3])) else t.contiguous() for t in tensors]
+    B, S, H, Dh = query.shape
+    dev = query.device
+    outs = [torch.empty(B, H, S, Dh, dtype=torch.bfloat16, device=dev) for _ in tensors]
+    p = _lib.PrepassParams()
+    p.q_in, p.k_in = tensors[0].data_ptr(), tensors[1].data_ptr()
+    p.q_out, p.k_out = outs[0].data_ptr(), outs[1].data_ptr()
+    for name, t in zip(("q", "k", "v"), tensors):
+        arr = getattr(p, name + "_strides")
+        arr[0], arr[1], arr[2] = t.stride()[:3]
+    if value is not None:
+        p.v_in, p.v_out = tensors[2].data_ptr(), outs[2].data_ptr()
+    keep = []
+    for name, wt in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if wt is not None:
+            wt = wt.to(device=dev, dtype=torch.float32).contiguous()
+            if wt.numel() != Dh:
+                raise ValueError(f"{name} must have {Dh} entries")
+            keep.append(wt)
+            setattr(p, name, wt.data_ptr())
+    if rope is not None:
+        cos, sin = (t.to(device=dev, dtype=torch.float32).contiguous() for t in rope)
+        if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[0] != S:
+            raise ValueError(f"rope tables must both be (seq={S}, rotary), got {tuple(cos.shape)} and {tuple(sin.shape)}")
+        keep += [cos, sin]
+        p.cos, p.sin, p.rotary = cos.data_ptr(), sin.data_ptr(), cos.shape[1]
+    kv_len_t = _kv_len_tensor(kv_len, B, dev)
+    p.kv_len = kv_len_t.data_ptr() if kv_len_t is not None else None
+    mk = None
+    if want_mk:
+        norms = torch.empty(2 * H, dtype=torch.float32, device=dev)
+        mk = torch.empty(2, H, dtype=torch.float32, device=dev)
+        keep.append(norms)
+        p.norms, p.mk_out = norms.data_ptr(), mk.data_ptr()
+    p.eps, p.scale, p.gate = float(eps), float(scale) if scale is not None else 0.0, float(gate)
+    p.B, p.S, p.H, p.D = B, S, H, Dh
+    with torch.cuda.device(dev):
+        st = _lib.load().dtb_qk_prepass(ctypes.byref(p), _stream_ptr(dev))
+    _lib.check(st, "dtb_qk_prepass")
+    return outs[0], outs[1], (outs[2] if value is not None else None), mk

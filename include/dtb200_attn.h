@@ -93,6 +93,22 @@ typedef struct dtb_scatter_heads_params {
   int32_t B, H, S_local, D;
 } dtb_scatter_heads_params;
 
+/* The step in front of the attention call in every DiT block: per-head RMSNorm of q and k, rotary embedding,
+ * zeroing of padded rows and the [B, S, H, D] -> [B, H, S, D] layout change, one read and one write per tensor.
+ * Strides are element strides of the (batch, sequence, head) axes of the inputs; outputs are contiguous [B, H, S, D]. */
+typedef struct dtb_prepass_params {
+  const void* q_in; const void* k_in; const void* v_in;   /* bf16 [B, S, H, D]; v_in may be NULL (then v_out too) */
+  int64_t q_strides[3], k_strides[3], v_strides[3];
+  void* q_out; void* k_out; void* v_out;                   /* bf16 [B, H, S, D] contiguous */
+  const float* q_weight; const float* k_weight;            /* RMSNorm scales [D], NULL = ones */
+  const float* cos; const float* sin;                      /* [S, rotary] f32, both NULL = no rotary embedding */
+  const int32_t* kv_len;                                   /* [B] or NULL: rows >= kv_len[b] are written as zeros */
+  float* norms;                                            /* scratch [2 * H] f32, required with mk_out */
+  float* mk_out;                                           /* [2, H] bounded-logit operand of the outputs, or NULL */
+  float eps, scale, gate;                                  /* scale <= 0: 1/sqrt(D); gate <= 0: 213 */
+  int32_t B, S, H, D, rotary;
+} dtb_prepass_params;
+
 /* Library version and a human-readable string for a status code. */
 int dtb_version(void);
 const char* dtb_status_string(int status);
@@ -152,6 +168,12 @@ int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float* norms, flo
  * may overlap on the GPU race and must be ordered by the caller.
  * This entry point has no counterpart in the reference project. */
 int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* stream);
+
+/* Fused q/k RMSNorm + rotary embedding + pad zeroing + layout change, optionally producing the bounded-logit
+ * operand of its outputs for free.  Replaces the per-block sequence diffusers_tpu/models/minimax_h3/jax_dit.py:362-388
+ * (norm_q / norm_k :191-195, apply_rope :251-262, pad zeroing :372-381, swapaxes :388), its torch twin
+ * diffusers_tpu/backends/ours_splash_tt.py:189-213, and the operand pass diffusers_tpu/kernels/fixed_m_bound.py:57-118. */
+int dtb_qk_prepass(const dtb_prepass_params* pp, void* stream);
 
 /* Hardware self-tests of the descriptor encodings the kernels rely on (one 128x128x128 tile each).
  * They write f32 [128,128] results for the host to compare; no reference counterpart. */

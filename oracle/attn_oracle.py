@@ -222,3 +222,40 @@ def merge_residuals(parts: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tens
     L = (w * ls).sum(0)
     O = (w.unsqueeze(-1) * os_).sum(0)
     return torch.where(L.unsqueeze(-1) > 0, O / L.unsqueeze(-1), torch.zeros(()))
+
+
+def qk_prepass(q: torch.Tensor, k: torch.Tensor, v: Optional[torch.Tensor] = None, *, q_weight=None, k_weight=None,
+               eps: float = 1e-5, rope=None, kv_len: KvLen = None):
+    """The block-level steps in front of the kernel, on CPU: RMSNorm per head, rotary embedding, pad zeroing and
+    the ``(B, S, H, D) -> (B, H, S, D)`` swap (diffusers_tpu/models/minimax_h3/jax_dit.py:191-195, 251-262, 362-388).
+
+    The norm is computed in f32 and cast to the input dtype; the rotation is applied to those bf16 values with the
+    tables cast to bf16, in f32 with one final rounding (the reference rounds after each bf16 operation on some
+    backends, which moves results by at most one bf16 ulp).
+    """
+    def norm(x, w):
+        x32 = x.float()
+        y = x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + eps)
+        if w is not None:
+            y = y * w.float()
+        return y.to(x.dtype)
+
+    def turn(x, cos, sin):
+        rotary = cos.shape[-1]
+        rotated, passed = x[..., :rotary].float(), x[..., rotary:]
+        c = cos.to(x.dtype).float()[None, :, None, :]
+        s = sin.to(x.dtype).float()[None, :, None, :]
+        x1, x2 = rotated.chunk(2, dim=-1)
+        turned = torch.cat([-x2, x1], dim=-1)
+        return torch.cat([(rotated * c + turned * s).to(x.dtype), passed], dim=-1)
+
+    qn, kn = norm(q, q_weight), norm(k, k_weight)
+    if rope is not None:
+        qn, kn = turn(qn, *rope), turn(kn, *rope)
+    outs = [qn, kn] + ([v] if v is not None else [])
+    if kv_len is not None:
+        lens = _kv_len_list(kv_len, q.shape[0], q.shape[1])
+        keep = (torch.arange(q.shape[1])[None, :] < torch.tensor(lens)[:, None])[:, :, None, None]
+        outs = [torch.where(keep, t, torch.zeros((), dtype=t.dtype)) for t in outs]
+    outs = [t.transpose(1, 2).contiguous() for t in outs]
+    return (outs[0], outs[1], outs[2] if v is not None else None)

@@ -123,3 +123,21 @@ def test_sampled_rows_match_full():
     full = O.attention_fp32(q, k, v, kv_len=150)
     part = O.attention_fp32(q, k, v, kv_len=150, rows=rows)
     assert torch.equal(part, full[:, :, rows])
+
+
+def test_prepass_oracle_properties():
+    # RMSNorm makes every kept row's mean square ~1 (unit weights), the rotation preserves each rotated pair's norm,
+    # channels past `rotary` pass through, padded rows are zero and the layout is (B, H, S, D).
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(2, 50, 3, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(2, 50, 3, 128, generator=g).to(torch.bfloat16)
+    ang = torch.arange(50, dtype=torch.float32)[:, None] * torch.linspace(0.01, 1.0, 48)[None, :]
+    cos, sin = torch.cat([ang.cos()] * 2, -1), torch.cat([ang.sin()] * 2, -1)
+    qn, kn, vn = O.qk_prepass(q, k, None, rope=(cos, sin), kv_len=[50, 31])
+    assert vn is None and qn.shape == (2, 3, 50, 128)
+    plain_q, _, _ = O.qk_prepass(q, k, None)
+    assert torch.allclose(plain_q.float().pow(2).mean(-1), torch.ones(2, 3, 50), atol=2e-2)
+    assert torch.equal(qn[0, :, :, 96:], plain_q[0, :, :, 96:])
+    pair = lambda t: t[..., :48].float().pow(2) + t[..., 48:96].float().pow(2)
+    assert torch.allclose(pair(qn[0]), pair(plain_q[0]), rtol=3e-2, atol=1e-3)
+    assert qn[1, :, 31:].abs().max() == 0 and kn[1, :, 31:].abs().max() == 0 and qn[1, :, :31].abs().max() > 0
