@@ -226,6 +226,11 @@ int fill_kernel_params(const dtb_attn_params* p, AttnKernelParams* kp) {
   kp->o_shard_rows = 0;
   kp->o_total_heads = 0;
   kp->o_head_offset = 0;
+  kp->kv_table = nullptr;
+  kp->kv_count = nullptr;
+  kp->head_class = nullptr;
+  kp->table_qblocks = 0;
+  kp->table_width = 0;
   return DTB_OK;
 }
 
@@ -491,4 +496,25 @@ extern "C" int dtb_scatter_heads(const dtb_scatter_heads_params* sp, void* strea
   const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((chunks + 255) / 256, 148 * 8));
   scatter_heads_kernel<<<dim3(blocks, sp->n_tensors), 256, 0, static_cast<cudaStream_t>(stream)>>>(kp);
   return launch_ok("scatter_heads_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
+}
+
+extern "C" int dtb_attn_fwd_sparse(const dtb_attn_params* p, const dtb_block_table* tb, void* stream) {
+  int st = check_params(p, true);
+  if (st != DTB_OK) return st;
+  if (tb == nullptr || tb->kv_table == nullptr || tb->kv_count == nullptr) return DTB_ERR_NULL;
+  if (tb->n_classes < 1 || tb->width < 1 || tb->q_blocks != q_blocks(p)) return DTB_ERR_SHAPE;
+  if (tb->n_classes > 1 && tb->head_class == nullptr) return DTB_ERR_NULL;
+  if (!device_is_sm100()) return DTB_ERR_ARCH;
+  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
+  AttnKernelParams kp;
+  st = fill_kernel_params(p, &kp);
+  if (st != DTB_OK) return st;
+  kp.kv_table = tb->kv_table;
+  kp.kv_count = tb->kv_count;
+  kp.head_class = tb->n_classes > 1 ? tb->head_class : nullptr;
+  kp.table_qblocks = tb->q_blocks;
+  kp.table_width = tb->width;
+  attn_fwd_kernel<false><<<dim3(q_blocks(p), p->Hq, p->B), dim3(kNumThreads), kSmemBytes,
+                           static_cast<cudaStream_t>(stream)>>>(kp);
+  return launch_ok("attn_fwd_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }

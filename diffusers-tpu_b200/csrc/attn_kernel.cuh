@@ -115,6 +115,12 @@ struct AttnKernelParams {
   // live on another GPU (plain peer stores), at head o_head_offset + h and row s % o_shard_rows.
   __nv_bfloat16* o_peer[8];
   int o_shard_rows, o_total_heads, o_head_offset;
+  // Block-sparse calls (kv_table != null): query block qb of a head in class c visits the key tiles
+  // kv_table[(c * table_qblocks + qb) * table_width + i], i < kv_count[c * table_qblocks + qb], ascending.
+  const int32_t* kv_table;
+  const int32_t* kv_count;
+  const int32_t* head_class;   // [Hq] or null (one class)
+  int table_qblocks, table_width;
 };
 
 // Warp-uniform bounded wait: every lane polls, and the warp agrees on the outcome so
@@ -247,7 +253,21 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   // Valid keys of this call: global indices [kv_offset, kv_offset + Skv) below kv_len[b].
   const int kv_len_b = (p.kv_len != nullptr) ? max(p.kv_len[b], 0) : 0x7fffffff;
   const int kv_eff = max(min(kv_len_b - p.kv_offset, p.Skv), 0);
-  const int n_total = (kv_eff + kBlockN - 1) / kBlockN;
+  // Key tiles this query block visits: all of [0, ceil(kv_eff / 128)) or, for a block-sparse call, the
+  // entries of its table row that start below kv_eff (the row is ascending: binary search).
+  const int32_t* tile_list = nullptr;
+  int n_total = (kv_eff + kBlockN - 1) / kBlockN;
+  if (p.kv_table != nullptr) {
+    const int cls = p.head_class != nullptr ? p.head_class[h] : 0;
+    const int64_t trow = static_cast<int64_t>(cls) * p.table_qblocks + blockIdx.x;
+    tile_list = p.kv_table + trow * p.table_width;
+    int lo = 0, hi = p.kv_count[trow];
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (tile_list[mid] * kBlockN < kv_eff) lo = mid + 1; else hi = mid;
+    }
+    n_total = lo;
+  }
   const int per_split = (n_total + p.num_splits - 1) / p.num_splits;
   const int tile_begin = min(split * per_split, n_total);
   const int tile_end = min(tile_begin + per_split, n_total);
@@ -339,7 +359,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         const uint32_t bar = smem_u32(&bars->kv_full[slot]);
         mbar_expect_tx(bar, kTileBytes);
         const uint32_t dst = smem_u32(smem_kv + slot * kTileBytes);
-        const int row = (tile_begin + (i >> 1)) * kBlockN;
+        const int entry = tile_begin + (i >> 1);
+        const int row = (tile_list != nullptr ? tile_list[entry] : entry) * kBlockN;
         const CUtensorMap* tm = (i & 1) ? &p.tmap_v : &p.tmap_k;
         tma_load_4d(dst, tm, bar, 0, row, hk, b);
         tma_load_4d(dst + kPanelBytes, tm, bar, 64, row, hk, b);
@@ -528,7 +549,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       DTB_PROF_END(0);
       if (!ok) break;
       tc_fence_after();
-      const int valid_cols = min(kv_eff - (tile_begin + j) * kBlockN, kBlockN);
+      const int tile = tile_list != nullptr ? tile_list[tile_begin + j] : tile_begin + j;
+      const int valid_cols = min(kv_eff - tile * kBlockN, kBlockN);
       if (fixed_m) {
         softmax_tile<true>(s_tmem, o_tmem, scale_log2, valid_cols, o_live, m_used, l_sum, bar_p_lo, bar_p_hi);
       } else {

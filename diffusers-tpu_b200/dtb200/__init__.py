@@ -12,7 +12,10 @@ from .ops import (  # noqa: F401
     check_device_status,
     finalize_residual,
     fixed_m_operands,
+    BlockTable,
+    make_block_table,
     qk_prepass,
+    sparse_attention,
     residual_attention,
     residual_attention_,
     sdpa,
@@ -20,5 +23,5 @@ from .ops import (  # noqa: F401
 
 __all__ = [
     "attention", "residual_attention", "residual_attention_", "finalize_residual", "fixed_m_operands",
-    "sdpa", "qk_prepass", "ResidualState", "check_device_status", "FIXED_M_SAFE_BOUND", "FIXED_M_RING_SAFE_BOUND",
+    "sdpa", "qk_prepass", "sparse_attention", "make_block_table", "BlockTable", "ResidualState", "check_device_status", "FIXED_M_SAFE_BOUND", "FIXED_M_RING_SAFE_BOUND",
 ]

@@ -25,7 +25,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 # Every symbol the public header declares; tests check that the library exports all of them.
 EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
-    "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_scatter_heads",
+    "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_attn_fwd_sparse", "dtb_scatter_heads",
     "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands", "dtb_qk_prepass",
     "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_mma_rate", "dtb_selftest_wait_timeout",
 )
@@ -78,6 +78,15 @@ class ScatterHeadsParams(ctypes.Structure):
     ]
 
 
+class BlockTable(ctypes.Structure):
+    """Mirror of ``dtb_block_table``."""
+
+    _fields_ = [
+        ("kv_table", ctypes.c_void_p), ("kv_count", ctypes.c_void_p), ("head_class", ctypes.c_void_p),
+        ("n_classes", ctypes.c_int32), ("q_blocks", ctypes.c_int32), ("width", ctypes.c_int32),
+    ]
+
+
 class PrepassParams(ctypes.Structure):
     """Mirror of ``dtb_prepass_params``."""
 
@@ -127,6 +136,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         lib.dtb_attn_fwd.argtypes = [ctypes.POINTER(AttnParams), vp, ctypes.c_size_t, vp]
         lib.dtb_attn_fwd_static_scratch.restype = ctypes.c_int
         lib.dtb_attn_fwd_static_scratch.argtypes = [ctypes.POINTER(AttnParams), vp]
+        lib.dtb_attn_fwd_sparse.restype = ctypes.c_int
+        lib.dtb_attn_fwd_sparse.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(BlockTable), vp]
         lib.dtb_qk_prepass.restype = ctypes.c_int
         lib.dtb_qk_prepass.argtypes = [ctypes.POINTER(PrepassParams), vp]
         lib.dtb_attn_fwd_scatter.restype = ctypes.c_int

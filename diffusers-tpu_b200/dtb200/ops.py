@@ -397,3 +397,102 @@ def qk_prepass(
         st = _lib.load().dtb_qk_prepass(ctypes.byref(p), _stream_ptr(dev))
     _lib.check(st, "dtb_qk_prepass")
     return outs[0], outs[1], (outs[2] if value is not None else None), mk
+
+
+class BlockTable:
+    """Device-resident block-sparsity table at the kernel's granularity (256 query rows x 128 keys).
+
+    Built once per layout with :func:`make_block_table` and passed to :func:`sparse_attention`.
+    """
+
+    def __init__(self, table: torch.Tensor, count: torch.Tensor, head_class: Optional[torch.Tensor], seq_q: int):
+        self.table, self.count, self.head_class, self.seq_q = table, count, head_class, seq_q
+        self.n_classes, self.q_blocks, self.width = table.shape
+
+
+def make_block_table(kv_table, *, seq_q: int, seq_kv: int, block_q: int, block_kv: int, device="cuda",
+                     heads: Optional[int] = None) -> BlockTable:
+    """Converts a reference-style table to the kernel's granularity and uploads it.
+
+    ``kv_table`` is what ``diffusers_tpu/kernels/sparse_splash.py:568-649`` takes: per query block of ``block_q``
+    rows the sorted list of key blocks (of ``block_kv`` keys) to visit, shared by all heads; or
+    ``(classes, head_class)`` with one such table per head class and a class index per head.  ``block_q`` must be a
+    multiple of 256 and ``block_kv`` a multiple of 128 (the kernel's tile), so that a reference block is a whole
+    number of kernel tiles; the result visits exactly the same (query, key) pairs.
+    """
+    if block_q % 256 or block_kv % 128:
+        raise NotImplementedError("block_q must be a multiple of 256 and block_kv a multiple of 128")
+    if isinstance(kv_table, tuple):
+        classes, head_class = kv_table
+        head_class = torch.as_tensor(list(head_class), dtype=torch.int32)
+        if heads is not None and head_class.numel() != heads:
+            raise ValueError("head_class must have one entry per head")
+    else:
+        classes, head_class = [kv_table], None
+    qb_ratio, kb_ratio = block_q // 256, block_kv // 128
+    n_q = (seq_q + 255) // 256
+    n_kv_tiles = (seq_kv + 127) // 128
+    rows = []
+    for table in classes:
+        if len(table) != (seq_q + block_q - 1) // block_q:
+            raise ValueError(f"table has {len(table)} query blocks, expected {(seq_q + block_q - 1) // block_q}")
+        per_q = []
+        for qb in range(n_q):
+            blocks = sorted(set(int(x) for x in table[qb // qb_ratio]))
+            tiles = [b * kb_ratio + i for b in blocks for i in range(kb_ratio) if b * kb_ratio + i < n_kv_tiles]
+            per_q.append(tiles)
+        rows.append(per_q)
+    width = max(1, max(len(t) for per_q in rows for t in per_q))
+    tab = torch.zeros(len(rows), n_q, width, dtype=torch.int32)
+    cnt = torch.zeros(len(rows), n_q, dtype=torch.int32)
+    for c, per_q in enumerate(rows):
+        for qb, tiles in enumerate(per_q):
+            cnt[c, qb] = len(tiles)
+            if tiles:
+                tab[c, qb, :len(tiles)] = torch.tensor(tiles, dtype=torch.int32)
+    return BlockTable(tab.to(device), cnt.to(device), head_class.to(device) if head_class is not None else None, seq_q)
+
+
+def sparse_attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    *,
+    kv_table: BlockTable,
+    scale: Optional[float] = None,
+    kv_len: KvLen = None,
+    use_fixed_m: bool = False,
+    mk: Optional[torch.Tensor] = None,
+    zero_padded_rows: bool = True,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Block-sparse joint attention: each query block attends only to the key tiles its table row lists.
+
+    Same contract as ``attention`` otherwise (``diffusers_tpu/kernels/sparse_splash.py:568-649``); a table that
+    lists every tile gives the dense result bit for bit.  Query blocks with an empty row come back as zeros.
+    """
+    _check_inputs(query, key, value)
+    query, key, value = _dense_last(query), _dense_last(key), _dense_last(value)
+    if kv_table.seq_q != query.shape[2]:
+        raise ValueError(f"table was built for seq_q={kv_table.seq_q}, got {query.shape[2]}")
+    if kv_table.head_class is not None and kv_table.head_class.numel() != query.shape[1]:
+        raise ValueError("table head classes do not match the number of heads")
+    dev = query.device
+    if out is None:
+        out = torch.empty(query.shape, dtype=query.dtype, device=dev)
+    kv_len_t = _kv_len_tensor(kv_len, query.shape[0], dev)
+    flags = _lib.FLAG_ZERO_PADDED_ROWS if (zero_padded_rows and kv_len_t is not None) else 0
+    if use_fixed_m:
+        if mk is None:
+            mk = fixed_m_operands(query, key, scale=scale)
+        flags |= _lib.FLAG_BOUNDED_LOGITS
+    else:
+        mk = None
+    p = _fill_params(query, key, value, out, kv_len_t, mk, scale, flags, 1, _status_buffer(dev))
+    tb = _lib.BlockTable(kv_table.table.data_ptr(), kv_table.count.data_ptr(),
+                         kv_table.head_class.data_ptr() if kv_table.head_class is not None else None,
+                         kv_table.n_classes, kv_table.q_blocks, kv_table.width)
+    with torch.cuda.device(dev):
+        st = _lib.load().dtb_attn_fwd_sparse(ctypes.byref(p), ctypes.byref(tb), _stream_ptr(dev))
+    _lib.check(st, "dtb_attn_fwd_sparse")
+    return out

@@ -109,6 +109,16 @@ typedef struct dtb_prepass_params {
   int32_t B, S, H, D, rotary;
 } dtb_prepass_params;
 
+/* Block-sparsity table at the kernel's own granularity (256 query rows x 128 keys): query block qb of a head in
+ * class c visits key tiles kv_table[(c * q_blocks + qb) * width + i] for i < kv_count[c * q_blocks + qb], in ascending
+ * order.  All arrays are int32 on the device; head_class ([Hq]) may be NULL when n_classes == 1. */
+typedef struct dtb_block_table {
+  const int32_t* kv_table;
+  const int32_t* kv_count;
+  const int32_t* head_class;
+  int32_t n_classes, q_blocks, width;
+} dtb_block_table;
+
 /* Library version and a human-readable string for a status code. */
 int dtb_version(void);
 const char* dtb_status_string(int status);
@@ -138,6 +148,11 @@ int dtb_attn_fwd_scatter(const dtb_attn_params* p, const dtb_attn_scatter* sc, v
  * diffusers_tpu/backends/qwen21_core_tt.py:108-115 (`_a2a` to heads).  The caller synchronises the ranks before
  * the destination buffers are read. */
 int dtb_scatter_heads(const dtb_scatter_heads_params* sp, void* stream);
+
+/* Block-sparse forward: the same arithmetic, but each query block only visits the key tiles its table row lists, so
+ * skipped tiles cost neither loads nor MMAs; a full table gives the dense result bit for bit.  kv_len still applies.
+ * Replaces diffusers_tpu/kernels/sparse_splash.py:568-649 `attention(..., kv_table= | kv_table_dyn=)`. */
+int dtb_attn_fwd_sparse(const dtb_attn_params* p, const dtb_block_table* tb, void* stream);
 
 /* Residual forward over one KV shard: folds this shard into the running (o_acc, m, l) state.
  * Replaces diffusers_tpu/kernels/splash.py:665-742 `residual_attention(...)` together with the

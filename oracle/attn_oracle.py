@@ -54,12 +54,23 @@ def _kv_len_list(kv_len: KvLen, batch: int, skv: int) -> list:
     return [max(0, min(v, skv)) for v in vals]
 
 
+def block_mask(kv_table, seq_q: int, seq_kv: int, block_q: int, block_kv: int) -> torch.Tensor:
+    """Boolean ``[seq_q, seq_kv]`` mask of the (query, key) pairs a block table visits
+    (diffusers_tpu/kernels/sparse_splash.py: per query block the sorted list of key blocks)."""
+    m = torch.zeros(seq_q, seq_kv, dtype=torch.bool)
+    for qb, blocks in enumerate(kv_table):
+        for kb in blocks:
+            m[qb * block_q:(qb + 1) * block_q, kb * block_kv:(kb + 1) * block_kv] = True
+    return m
+
+
 def attention_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Optional[float] = None,
                    kv_len: KvLen = None, zero_padded_rows: bool = True, rows: Optional[torch.Tensor] = None,
-                   out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                   out_dtype: torch.dtype = torch.float32, mask=None) -> torch.Tensor:
     """fp32-softmax attention on CPU, one (batch, head) at a time to bound memory.
 
-    ``rows`` (1-D long tensor) restricts the computation to those query rows (sampled-row
+    ``mask`` (bool ``[Sq, Skv]``, or one per head) restricts the keys each query sees (block-sparse calls); queries
+    that see no key give zeros.  ``rows`` (1-D long tensor) restricts the computation to those query rows (sampled-row
     checks of long sequences); the result then has ``len(rows)`` rows.  Query rows at or past
     ``kv_len[b]`` are zero when ``zero_padded_rows`` (the callers of the reference zero padded
     queries: diffusers_tpu/models/minimax_h3/jax_dit.py:374-381).
@@ -81,8 +92,16 @@ def attention_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: 
             kf = k[b, h // group, :n].float()
             vf = v[b, h // group, :n].float()
             logits = (qf @ kf.T) * s
+            if mask is not None:
+                mh = mask[h] if isinstance(mask, (list, tuple)) else mask
+                mh = mh.index_select(0, ridx)[:, :n]
+                logits = logits.masked_fill(~mh, float("-inf"))
+                dead = ~mh.any(dim=-1)
+                logits[dead] = 0.0
             p = torch.softmax(logits, dim=-1)
             o = p @ vf
+            if mask is not None:
+                o[dead] = 0
             if zero_padded_rows and kv_len is not None:
                 o[ridx >= n] = 0
             out[b, h] = o
