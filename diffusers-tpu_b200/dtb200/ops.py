@@ -357,7 +357,8 @@ def qk_prepass(
             raise NotImplementedError(f"expected bf16 (B, S, H, 128), got {t.dtype} {tuple(t.shape)}")
         if t.shape != query.shape:
             raise ValueError("query, key and value must have the same shape")
-    tensors = [t if (t.stride(-1) == 1 and all(s % 4 == 0 for s in t.stride()[:3])) else t.contiguous() for t in tensors]
+    tensors = [t if (t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3]))
+               else t.contiguous() for t in tensors]
     B, S, H, Dh = query.shape
     dev = query.device
     outs = [torch.empty(B, H, S, Dh, dtype=torch.bfloat16, device=dev) for _ in tensors]

@@ -101,7 +101,7 @@ typedef struct dtb_prepass_params {
   int64_t q_strides[3], k_strides[3], v_strides[3];
   void* q_out; void* k_out; void* v_out;                   /* bf16 [B, H, S, D] contiguous */
   const float* q_weight; const float* k_weight;            /* RMSNorm scales [D], NULL = ones */
-  const float* cos; const float* sin;                      /* [S, rotary] f32, both NULL = no rotary embedding */
+  const float* cos; const float* sin;                      /* [S, rotary] f32 (rotary % 16 == 0), both NULL = none */
   const int32_t* kv_len;                                   /* [B] or NULL: rows >= kv_len[b] are written as zeros */
   float* norms;                                            /* scratch [2 * H] f32, required with mk_out */
   float* mk_out;                                           /* [2, H] bounded-logit operand of the outputs, or NULL */
