@@ -28,9 +28,14 @@ struct PrepassParams {
   int B, S, H, rotary, n_tensors;
 };
 
-// Half a warp owns a row: lane l of the half owns elements 8l..8l+7 (one 16-byte access).  A warp works on
-// kRowsInFlight rows at a time so that several independent 256-byte reads are outstanding per warp.
-constexpr int kRowsInFlight = 4;
+// Half a warp owns a row: lane l of the half owns elements 8l..8l+7 (one 16-byte access).  A block of 8 warps
+// takes 8 consecutive positions of one batch element, one position per warp, and walks the heads eight at a
+// time (two rows per warp access, four accesses in flight): a warp reads 1 KB of contiguous [B, S, H, D] input per
+// step and the block writes 2 KB of contiguous [B, H, S, D] output per head, and the rotary table row of the
+// position is loaded once per warp and reused for every head.  Per-head norm maxima are kept in shared memory
+// and flushed once per block.
+constexpr int kTilePositions = 8;
+constexpr int kAccessesInFlight = 4;   // 16-byte loads outstanding per lane (two rows each per warp)
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float (&x)[8]) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -48,118 +53,114 @@ __device__ __forceinline__ float half_warp_sum(float v) {
   return v;
 }
 
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16(v)); }
+
 __global__ void __launch_bounds__(256) qk_prepass_kernel(const __grid_constant__ PrepassParams p) {
+  extern __shared__ int head_max[];                   // [H] row-norm maxima (as int bits) of this block
   const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
   const int hl = lane & 15;                           // lane within the half warp
   const int sub = lane >> 4;                          // which of the two rows of a warp access
   const int which = blockIdx.y;                       // 0 = q, 1 = k, 2 = v
-  const int64_t rows = static_cast<int64_t>(p.B) * p.H * p.S;
-  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * 8;
+  const bool want_norms = which < 2 && p.norms != nullptr;
   const int half_lanes = p.rotary / 16;               // lanes holding one half of the rotated channels
-  float best = 0.f;
-  int best_h = -1;
+  const bool first = hl < half_lanes;
+  const bool second = hl >= half_lanes && hl < 2 * half_lanes;
+  const int partner = (lane & 16) | ((first ? hl + half_lanes : hl - half_lanes) & 15);
+  const int s_tiles = (p.S + kTilePositions - 1) / kTilePositions;
+  const int64_t tiles = static_cast<int64_t>(p.B) * s_tiles;
+  if (want_norms) {
+    for (int i = threadIdx.x; i < p.H; i += blockDim.x) head_max[i] = 0;
+    __syncthreads();
+  }
   float wgt[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
   if (which < 2 && p.weight[which] != nullptr) {
     const float4 a = reinterpret_cast<const float4*>(p.weight[which])[2 * hl];
     const float4 c = reinterpret_cast<const float4*>(p.weight[which])[2 * hl + 1];
     wgt[0] = a.x; wgt[1] = a.y; wgt[2] = a.z; wgt[3] = a.w; wgt[4] = c.x; wgt[5] = c.y; wgt[6] = c.z; wgt[7] = c.w;
   }
-  // rows are visited in output order (b, h, s): a warp mostly stays inside one head
-  for (int64_t base = (static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * kRowsInFlight; base < rows;
-       base += warps_total * kRowsInFlight) {
-    uint4 raw[kRowsInFlight / 2];
-    bool live[kRowsInFlight / 2];
-    int hh[kRowsInFlight / 2], ss[kRowsInFlight / 2];
+  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const int b = static_cast<int>(tile / s_tiles);
+    const int s = static_cast<int>(tile % s_tiles) * kTilePositions + warp;
+    if (s >= p.S) continue;                           // warp-uniform
+    const bool live = p.kv_len == nullptr || s < p.kv_len[b];
+    float cs[8], sn[8];
+    if (which < 2 && p.cos != nullptr && (first || second)) {
+      // tables are used in the input dtype, as the reference casts them
+      const float4* cp = reinterpret_cast<const float4*>(p.cos + static_cast<int64_t>(s) * p.rotary) + 2 * hl;
+      const float4* sp = reinterpret_cast<const float4*>(p.sin + static_cast<int64_t>(s) * p.rotary) + 2 * hl;
+      const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+      cs[0] = round_bf16(c0.x); cs[1] = round_bf16(c0.y); cs[2] = round_bf16(c0.z); cs[3] = round_bf16(c0.w);
+      cs[4] = round_bf16(c1.x); cs[5] = round_bf16(c1.y); cs[6] = round_bf16(c1.z); cs[7] = round_bf16(c1.w);
+      sn[0] = round_bf16(s0.x); sn[1] = round_bf16(s0.y); sn[2] = round_bf16(s0.z); sn[3] = round_bf16(s0.w);
+      sn[4] = round_bf16(s1.x); sn[5] = round_bf16(s1.y); sn[6] = round_bf16(s1.z); sn[7] = round_bf16(s1.w);
+      if (first) {
 #pragma unroll
-    for (int u = 0; u < kRowsInFlight / 2; ++u) {
-      const int64_t rid = base + 2 * u + sub;
-      const bool in = rid < rows;
-      const int64_t r = in ? rid : 0;
-      const int s = static_cast<int>(r % p.S);
-      const int h = static_cast<int>((r / p.S) % p.H);
-      const int b = static_cast<int>(r / (static_cast<int64_t>(p.S) * p.H));
-      hh[u] = h;
-      ss[u] = s;
-      live[u] = in && !(p.kv_len != nullptr && s >= p.kv_len[b]);
-      raw[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (live[u])
-        raw[u] = reinterpret_cast<const uint4*>(p.in[which] + b * p.sb[which] + s * p.ss[which] + h * p.sh[which])[hl];
+        for (int i = 0; i < 8; ++i) sn[i] = -sn[i];   // turned = (-second half, first half)
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { cs[i] = 1.f; sn[i] = 0.f; }
     }
+    const __nv_bfloat16* in_row = p.in[which] + b * p.sb[which] + s * p.ss[which];
+    __nv_bfloat16* out_row = p.out[which] + (static_cast<int64_t>(b) * p.H * p.S + s) * kD;
+    for (int h0 = 0; h0 < p.H; h0 += 2 * kAccessesInFlight) {
+      uint4 raw[kAccessesInFlight];
+      int hh[kAccessesInFlight];
 #pragma unroll
-    for (int u = 0; u < kRowsInFlight / 2; ++u) {
-      const int64_t rid = base + 2 * u + sub;
-      uint4 packed = raw[u];
-      if (which < 2) {
-        float x[8];
-        unpack8(raw[u], x);
-        float ssq = 0.f;
+      for (int u = 0; u < kAccessesInFlight; ++u) {
+        hh[u] = h0 + 2 * u + sub;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (live && hh[u] < p.H) raw[u] = reinterpret_cast<const uint4*>(in_row + hh[u] * p.sh[which])[hl];
+      }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ssq += x[i] * x[i];
-        ssq = half_warp_sum(ssq);
-        const float rrms = rsqrtf(ssq * (1.0f / kD) + p.eps);
-        float y[8];
+      for (int u = 0; u < kAccessesInFlight; ++u) {
+        uint4 packed = raw[u];
+        if (which < 2) {
+          float x[8];
+          unpack8(raw[u], x);
+          float ssq = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i)   // normalised value, rounded to bf16 as the reference's RMSNorm returns it
-          y[i] = __bfloat162float(__float2bfloat16(x[i] * rrms * wgt[i]));
-        if (p.cos != nullptr) {
-          // channel c < rotary/2 pairs with c + rotary/2: out = y*cos + turned*sin, turned = (-second half, first half)
-          const bool first = hl < half_lanes;
-          const bool second = hl >= half_lanes && hl < 2 * half_lanes;
-          const int partner = (first ? hl + half_lanes : hl - half_lanes) & 15;
-          float other[8];
+          for (int i = 0; i < 8; ++i) ssq += x[i] * x[i];
+          ssq = half_warp_sum(ssq);
+          const float rrms = rsqrtf(ssq * (1.0f / kD) + p.eps);
+          float y[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) other[i] = __shfl_sync(0xffffffffu, y[i], (lane & 16) | partner);
-          if ((first || second) && live[u]) {
-            const float4* cp = reinterpret_cast<const float4*>(p.cos + static_cast<int64_t>(ss[u]) * p.rotary) + 2 * hl;
-            const float4* sp = reinterpret_cast<const float4*>(p.sin + static_cast<int64_t>(ss[u]) * p.rotary) + 2 * hl;
-            const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
-            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+          for (int i = 0; i < 8; ++i)   // normalised value, rounded to bf16 as the reference's RMSNorm returns it
+            y[i] = round_bf16(x[i] * rrms * wgt[i]);
+          if (p.cos != nullptr) {
+            // channel c < rotary/2 pairs with c + rotary/2: out = y*cos + turned*sin
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const float cb = __bfloat162float(__float2bfloat16(cs[i]));   // tables are used in the input dtype
-              const float sb_ = __bfloat162float(__float2bfloat16(sn[i]));
-              y[i] = y[i] * cb + (first ? -other[i] : other[i]) * sb_;
+              const float other = __shfl_sync(0xffffffffu, y[i], partner);
+              y[i] = y[i] * cs[i] + other * sn[i];
             }
           }
-        }
-        packed.x = pack_bf16x2(y[0], y[1]);
-        packed.y = pack_bf16x2(y[2], y[3]);
-        packed.z = pack_bf16x2(y[4], y[5]);
-        packed.w = pack_bf16x2(y[6], y[7]);
-        if (!live[u]) packed = make_uint4(0u, 0u, 0u, 0u);
-        if (p.norms != nullptr) {
-          float z[8];
-          unpack8(packed, z);
-          float n2 = 0.f;
+          packed.x = pack_bf16x2(y[0], y[1]);
+          packed.y = pack_bf16x2(y[2], y[3]);
+          packed.z = pack_bf16x2(y[4], y[5]);
+          packed.w = pack_bf16x2(y[6], y[7]);
+          if (!live) packed = make_uint4(0u, 0u, 0u, 0u);
+          if (want_norms) {
+            float z[8];
+            unpack8(packed, z);
+            float n2 = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) n2 += z[i] * z[i];
-          n2 = half_warp_sum(n2);
-          const float nrm = sqrtf(n2) * (which == 0 ? p.q_norm_mult : 1.0f);
-          // fold both rows of the warp access into the running per-head maximum kept by lane 0
-          const float n_lo = __shfl_sync(0xffffffffu, nrm, 0), n_hi = __shfl_sync(0xffffffffu, nrm, 16);
-          const int h_lo = __shfl_sync(0xffffffffu, hh[u], 0), h_hi = __shfl_sync(0xffffffffu, hh[u], 16);
-          const bool in_hi = __shfl_sync(0xffffffffu, static_cast<int>(rid < rows), 16) != 0;
-          const bool in_lo = __shfl_sync(0xffffffffu, static_cast<int>(rid < rows), 0) != 0;
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int h = e ? h_hi : h_lo;
-            const float n = e ? n_hi : n_lo;
-            if (!(e ? in_hi : in_lo)) continue;
-            if (h != best_h) {
-              if (best_h >= 0 && lane == 0) atomicMax(reinterpret_cast<int*>(p.norms + which * p.H + best_h), __float_as_int(best));
-              best_h = h;
-              best = 0.f;
-            }
-            best = fmaxf(best, n);
+            for (int i = 0; i < 8; ++i) n2 += z[i] * z[i];
+            n2 = half_warp_sum(n2);
+            if (hl == 0 && live && hh[u] < p.H)
+              atomicMax(&head_max[hh[u]], __float_as_int(sqrtf(n2) * (which == 0 ? p.q_norm_mult : 1.0f)));
           }
         }
+        if (hh[u] < p.H) reinterpret_cast<uint4*>(out_row + static_cast<int64_t>(hh[u]) * p.S * kD)[hl] = packed;
       }
-      if (rid < rows) reinterpret_cast<uint4*>(p.out[which] + rid * kD)[hl] = packed;
     }
   }
-  if (which < 2 && p.norms != nullptr && best_h >= 0 && lane == 0)
-    atomicMax(reinterpret_cast<int*>(p.norms + which * p.H + best_h), __float_as_int(best));
+  if (want_norms) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.H; i += blockDim.x)
+      if (head_max[i] != 0) atomicMax(reinterpret_cast<int*>(p.norms + which * p.H + i), head_max[i]);
+  }
 }
 
 __global__ void prepass_bound_kernel(const float* __restrict__ norms, int H, float gate, float* __restrict__ mk) {
@@ -217,9 +218,10 @@ extern "C" int dtb_qk_prepass(const dtb_prepass_params* pp, void* stream) {
   if (pp->norms != nullptr &&
       !cuda_ok(cudaMemsetAsync(pp->norms, 0, sizeof(float) * 2 * pp->H, s), "cudaMemsetAsync(norms)"))
     return DTB_ERR_LAUNCH;
-  const int64_t rows = static_cast<int64_t>(pp->B) * pp->H * pp->S;
-  const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((rows + 31) / 32, 148 * 16));
-  qk_prepass_kernel<<<dim3(blocks, kp.n_tensors), 256, 0, s>>>(kp);
+  if (pp->H > 8192) return DTB_ERR_SHAPE;
+  const int64_t tiles = static_cast<int64_t>(pp->B) * ((pp->S + 7) / 8);
+  const unsigned blocks = static_cast<unsigned>(std::min<int64_t>(tiles, 148 * 8));
+  qk_prepass_kernel<<<dim3(blocks, kp.n_tensors), 256, sizeof(int) * pp->H, s>>>(kp);
   if (!launch_ok("qk_prepass_kernel launch")) return DTB_ERR_LAUNCH;
   if (pp->mk_out != nullptr) {
     prepass_bound_kernel<<<(pp->H + 127) / 128, 128, 0, s>>>(pp->norms, pp->H, pp->gate > 0.f ? pp->gate : 213.0f,
