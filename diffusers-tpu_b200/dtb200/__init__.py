@@ -4,6 +4,7 @@ A drop-in for the device-local attention entry points of shungcp/diffusers-tpu
 (``diffusers_tpu.kernels.splash.attention`` / ``residual_attention`` and the SDPA callable of
 ``diffusers_tpu.kernels.mesh_attention``), backed by hand-written sm_100a kernels behind a C ABI.
 """
+from . import fixed_m  # noqa: F401
 from .ops import (  # noqa: F401
     FIXED_M_RING_SAFE_BOUND,
     FIXED_M_SAFE_BOUND,
