@@ -7,6 +7,8 @@
 #include <cstdio>
 #include <mutex>
 
+#include <cuda_fp8.h>
+
 #include "attn_kernel.cuh"
 #include "host_common.h"
 
@@ -155,7 +157,7 @@ int q_blocks(const dtb_attn_params* p) { return (p->Sq + kQTiles * kBlockM - 1) 
 // Split-KV factor.  Splitting pays when the (batch, head, query-block) grid leaves
 // most SMs idle and each CTA would otherwise sweep many key tiles alone.
 int resolve_splits(const dtb_attn_params* p) {
-  if (p->num_splits == 1) return 1;
+  if (p->num_splits == 1 || (p->flags & DTB_FLAG_QK_FP8)) return 1;
   const int kv_tiles = (p->Skv + kBlockN - 1) / kBlockN;
   int n = p->num_splits;
   if (n <= 0) {
@@ -182,10 +184,13 @@ cudaError_t ensure_kernel_attrs() {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64 && g_attrs_set[dev].load(std::memory_order_acquire)) return cudaSuccess;
-  e = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  e = cudaFuncSetAttribute(attn_fwd_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(kSmemBytes));
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  e = cudaFuncSetAttribute(attn_fwd_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kSmemBytes));
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(attn_fwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(kSmemBytes));
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64) g_attrs_set[dev].store(true, std::memory_order_release);
@@ -193,11 +198,16 @@ cudaError_t ensure_kernel_attrs() {
 }
 
 int fill_kernel_params(const dtb_attn_params* p, AttnKernelParams* kp) {
-  int st = make_tmap_bhsd(&kp->tmap_q, p->q, p->B, p->Hq, p->Sq, p->q_stride_b, p->q_stride_h, p->q_stride_s,
-                          kBlockM);
+  const bool fp8 = (p->flags & DTB_FLAG_QK_FP8) != 0;
+  int st = fp8 ? make_tmap_bhsd_u8(&kp->tmap_q, p->q, p->B, p->Hq, p->Sq, p->q_stride_b, p->q_stride_h, p->q_stride_s,
+                                   kBlockM)
+               : make_tmap_bhsd(&kp->tmap_q, p->q, p->B, p->Hq, p->Sq, p->q_stride_b, p->q_stride_h, p->q_stride_s,
+                                kBlockM);
   if (st != DTB_OK) return st;
-  st = make_tmap_bhsd(&kp->tmap_k, p->k, p->B, p->Hkv, p->Skv, p->k_stride_b, p->k_stride_h, p->k_stride_s,
-                      kBlockN);
+  st = fp8 ? make_tmap_bhsd_u8(&kp->tmap_k, p->k, p->B, p->Hkv, p->Skv, p->k_stride_b, p->k_stride_h, p->k_stride_s,
+                               kBlockN)
+           : make_tmap_bhsd(&kp->tmap_k, p->k, p->B, p->Hkv, p->Skv, p->k_stride_b, p->k_stride_h, p->k_stride_s,
+                            kBlockN);
   if (st != DTB_OK) return st;
   st = make_tmap_bhsd(&kp->tmap_v, p->v, p->B, p->Hkv, p->Skv, p->v_stride_b, p->v_stride_h, p->v_stride_s,
                       kBlockN);
@@ -271,9 +281,15 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
     }
   }
   const dim3 block(kNumThreads);
+  if (p->flags & DTB_FLAG_QK_FP8) {
+    // E4M3 q/k: one kernel variant, no split-KV
+    if (p->num_splits > 1) return DTB_ERR_UNSUPPORTED;
+    attn_fwd_kernel<false, true><<<dim3(q_blocks(p), p->Hq, p->B), block, kSmemBytes, s>>>(kp);
+    return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
+  }
   if (splits == 1) {
     const dim3 grid(q_blocks(p), p->Hq, p->B);
-    attn_fwd_kernel<false><<<grid, block, kSmemBytes, s>>>(kp);
+    attn_fwd_kernel<false, false><<<grid, block, kSmemBytes, s>>>(kp);
     return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
   }
   const size_t rows = static_cast<size_t>(splits) * p->B * p->Hq * p->Sq;
@@ -283,7 +299,7 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
   kp.num_splits = splits;
   kp.acc_init = 1;
   const dim3 grid(q_blocks(p), p->Hq, p->B * splits);
-  attn_fwd_kernel<true><<<grid, block, kSmemBytes, s>>>(kp);
+  attn_fwd_kernel<true, false><<<grid, block, kSmemBytes, s>>>(kp);
   if (!launch_ok("attn_fwd_kernel launch")) return DTB_ERR_LAUNCH;
   const int64_t out_rows = static_cast<int64_t>(p->B) * p->Hq * p->Sq;
   combine_kernel<<<static_cast<unsigned>((out_rows + 7) / 8), 256, 0, s>>>(
@@ -295,6 +311,7 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
 extern "C" int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_residual* r, void* stream) {
   int st = check_params(p, false);
   if (st != DTB_OK) return st;
+  if (p->flags & DTB_FLAG_QK_FP8) return DTB_ERR_UNSUPPORTED;
   if (r == nullptr || r->o_acc == nullptr || r->m == nullptr || r->l == nullptr) return DTB_ERR_NULL;
   if (reinterpret_cast<uintptr_t>(r->o_acc) & 15u) return DTB_ERR_ALIGN;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
@@ -310,7 +327,7 @@ extern "C" int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_re
   kp.acc_init = r->init ? 1 : 0;
   kp.zero_padded_rows = 0;  // padded rows are zeroed by dtb_attn_finalize
   const dim3 grid(q_blocks(p), p->Hq, p->B);
-  attn_fwd_kernel<true><<<grid, dim3(kNumThreads), kSmemBytes, static_cast<cudaStream_t>(stream)>>>(kp);
+  attn_fwd_kernel<true, false><<<grid, dim3(kNumThreads), kSmemBytes, static_cast<cudaStream_t>(stream)>>>(kp);
   return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
 
@@ -330,6 +347,7 @@ extern "C" int dtb_attn_finalize(const dtb_attn_params* p, const dtb_attn_residu
 extern "C" int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float* norms, float* mk_out, void* stream) {
   int st = check_params(p, false);
   if (st != DTB_OK) return st;
+  if (p->flags & DTB_FLAG_QK_FP8) return DTB_ERR_UNSUPPORTED;
   if (norms == nullptr || mk_out == nullptr) return DTB_ERR_NULL;
   if ((reinterpret_cast<uintptr_t>(p->q) & 7u) || (reinterpret_cast<uintptr_t>(p->k) & 7u)) return DTB_ERR_ALIGN;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -391,6 +409,7 @@ int static_scratch_address(void** out) {
 extern "C" int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* stream) {
   int st = check_params(p, true);
   if (st != DTB_OK) return st;
+  if (p->flags & DTB_FLAG_QK_FP8) return DTB_ERR_UNSUPPORTED;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
   const int splits = resolve_splits(p);
   const size_t need = splits > 1 ? split_workspace_bytes(p, splits) : 0;
@@ -411,7 +430,7 @@ extern "C" int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* strea
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 block(kNumThreads);
   if (splits == 1) {
-    attn_fwd_kernel<false><<<dim3(q_blocks(p), p->Hq, p->B), block, kSmemBytes, s>>>(kp);
+    attn_fwd_kernel<false, false><<<dim3(q_blocks(p), p->Hq, p->B), block, kSmemBytes, s>>>(kp);
     return launch_ok("attn_fwd_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
   }
   const size_t rows = static_cast<size_t>(splits) * p->B * p->Hq * p->Sq;
@@ -420,7 +439,7 @@ extern "C" int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* strea
   kp.acc_l = kp.acc_m + rows;
   kp.num_splits = splits;
   kp.acc_init = 1;
-  attn_fwd_kernel<true><<<dim3(q_blocks(p), p->Hq, p->B * splits), block, kSmemBytes, s>>>(kp);
+  attn_fwd_kernel<true, false><<<dim3(q_blocks(p), p->Hq, p->B * splits), block, kSmemBytes, s>>>(kp);
   if (!launch_ok("attn_fwd_kernel launch")) return DTB_ERR_LAUNCH;
   const int64_t out_rows = static_cast<int64_t>(p->B) * p->Hq * p->Sq;
   combine_kernel<<<static_cast<unsigned>((out_rows + 7) / 8), 256, 0, s>>>(
@@ -442,6 +461,7 @@ extern "C" int dtb_debug_read_wait_profile(unsigned long long* out) {
 extern "C" int dtb_attn_fwd_scatter(const dtb_attn_params* p, const dtb_attn_scatter* sc, void* stream) {
   int st = check_params(p, false);
   if (st != DTB_OK) return st;
+  if (p->flags & DTB_FLAG_QK_FP8) return DTB_ERR_UNSUPPORTED;
   if (sc == nullptr) return DTB_ERR_NULL;
   if (sc->n_peers < 1 || sc->n_peers > 8 || sc->shard_rows <= 0 || sc->total_heads < p->Hq || sc->head_offset < 0 ||
       sc->head_offset + p->Hq > sc->total_heads)
@@ -460,7 +480,7 @@ extern "C" int dtb_attn_fwd_scatter(const dtb_attn_params* p, const dtb_attn_sca
   kp.o_shard_rows = sc->shard_rows;
   kp.o_total_heads = sc->total_heads;
   kp.o_head_offset = sc->head_offset;
-  attn_fwd_kernel<false><<<dim3(q_blocks(p), p->Hq, p->B), dim3(kNumThreads), kSmemBytes,
+  attn_fwd_kernel<false, false><<<dim3(q_blocks(p), p->Hq, p->B), dim3(kNumThreads), kSmemBytes,
                            static_cast<cudaStream_t>(stream)>>>(kp);
   return launch_ok("attn_fwd_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
@@ -501,6 +521,7 @@ extern "C" int dtb_scatter_heads(const dtb_scatter_heads_params* sp, void* strea
 extern "C" int dtb_attn_fwd_sparse(const dtb_attn_params* p, const dtb_block_table* tb, void* stream) {
   int st = check_params(p, true);
   if (st != DTB_OK) return st;
+  if (p->flags & DTB_FLAG_QK_FP8) return DTB_ERR_UNSUPPORTED;
   if (tb == nullptr || tb->kv_table == nullptr || tb->kv_count == nullptr) return DTB_ERR_NULL;
   if (tb->n_classes < 1 || tb->width < 1 || tb->q_blocks != q_blocks(p)) return DTB_ERR_SHAPE;
   if (tb->n_classes > 1 && tb->head_class == nullptr) return DTB_ERR_NULL;
@@ -514,7 +535,55 @@ extern "C" int dtb_attn_fwd_sparse(const dtb_attn_params* p, const dtb_block_tab
   kp.head_class = tb->n_classes > 1 ? tb->head_class : nullptr;
   kp.table_qblocks = tb->q_blocks;
   kp.table_width = tb->width;
-  attn_fwd_kernel<false><<<dim3(q_blocks(p), p->Hq, p->B), dim3(kNumThreads), kSmemBytes,
+  attn_fwd_kernel<false, false><<<dim3(q_blocks(p), p->Hq, p->B), dim3(kNumThreads), kSmemBytes,
                            static_cast<cudaStream_t>(stream)>>>(kp);
   return launch_ok("attn_fwd_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Saturating E4M3 cast of a bf16 [B, H, S, 128] tensor (values are multiplied by `mult` first, beyond +-448 they
+// clamp instead of overflowing), written contiguously.  8 elements per thread.
+// ---------------------------------------------------------------------------------------------
+namespace dtb {
+namespace {
+__global__ void __launch_bounds__(256) quantize_e4m3_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh,
+                                                            int64_t ss, int B, int H, int S, float mult,
+                                                            uint8_t* __restrict__ out) {
+  const int64_t chunks = static_cast<int64_t>(B) * H * S * 16;   // 8 elements each
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < chunks;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(idx & 15);
+    const int64_t rowid = idx >> 4;
+    const int s = static_cast<int>(rowid % S);
+    const int h = static_cast<int>((rowid / S) % H);
+    const int b = static_cast<int>(rowid / (static_cast<int64_t>(S) * H));
+    const uint4 raw = reinterpret_cast<const uint4*>(x + b * sb + h * sh + s * ss)[c];
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      f.x *= mult;
+      f.y *= mult;
+      const uint32_t two = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+      packed[i >> 1] |= two << (16 * (i & 1));
+    }
+    reinterpret_cast<uint2*>(out + rowid * kHeadDim)[c] = make_uint2(packed[0], packed[1]);
+  }
+}
+}  // namespace
+}  // namespace dtb
+
+extern "C" int dtb_quantize_e4m3(const void* x, int64_t stride_b, int64_t stride_h, int64_t stride_s, int32_t B, int32_t H,
+                                 int32_t S, int32_t D, float mult, void* out, void* stream) {
+  if (x == nullptr || out == nullptr) return DTB_ERR_NULL;
+  if (D != kHeadDim || B <= 0 || H <= 0 || S <= 0) return DTB_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(out) & 7u) || (stride_b & 7) || (stride_h & 7) ||
+      (stride_s & 7))
+    return DTB_ERR_ALIGN;
+  const int64_t chunks = static_cast<int64_t>(B) * H * S * 16;
+  const unsigned blocks = static_cast<unsigned>(std::min<int64_t>((chunks + 255) / 256, 148 * 16));
+  quantize_e4m3_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), stride_b, stride_h, stride_s, B, H, S, mult, static_cast<uint8_t*>(out));
+  return launch_ok("quantize_e4m3_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }

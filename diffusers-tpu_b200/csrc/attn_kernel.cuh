@@ -230,8 +230,11 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
 //              kResidual = true : fold into / emit the running (o, m, l) state
 //                                 (ring steps and split-KV partials).
 // ---------------------------------------------------------------------------
-template <bool kResidual>
+//              kQkFp8 = true    : q and k are E4M3 bytes ([B, H, S, 128] with byte strides); the score MMA runs as
+//                                 kind::f8f6f4 with 32 contraction elements per instruction, P*V stays bf16.
+template <bool kResidual, bool kQkFp8>
 __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnKernelParams p) {
+  constexpr uint32_t kQkTileBytes = kQkFp8 ? kPanelBytes : kTileBytes;   // bytes of one 128-row Q or K tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem;
   {
@@ -344,10 +347,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     if (lane == 0) {
       for (int t = 0; t < kQTiles; ++t) {
         const uint32_t bar = smem_u32(&bars->q_full[t]);
-        mbar_expect_tx(bar, kTileBytes);
+        mbar_expect_tx(bar, kQkTileBytes);
         const uint32_t dst = smem_u32(smem_q + t * kTileBytes);
         tma_load_4d(dst, &p.tmap_q, bar, 0, q0 + t * kBlockM, h, b);
-        tma_load_4d(dst + kPanelBytes, &p.tmap_q, bar, 64, q0 + t * kBlockM, h, b);
+        if (!kQkFp8) tma_load_4d(dst + kPanelBytes, &p.tmap_q, bar, 64, q0 + t * kBlockM, h, b);
       }
       for (int i = 0; i < 2 * n_tiles && ok; ++i) {
         const int slot = i % kStages;
@@ -357,13 +360,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         DTB_PROF_END(0);
         if (!ok) break;
         const uint32_t bar = smem_u32(&bars->kv_full[slot]);
-        mbar_expect_tx(bar, kTileBytes);
+        const bool is_v = (i & 1) != 0;
+        mbar_expect_tx(bar, is_v ? kTileBytes : kQkTileBytes);
         const uint32_t dst = smem_u32(smem_kv + slot * kTileBytes);
         const int entry = tile_begin + (i >> 1);
         const int row = (tile_list != nullptr ? tile_list[entry] : entry) * kBlockN;
-        const CUtensorMap* tm = (i & 1) ? &p.tmap_v : &p.tmap_k;
+        const CUtensorMap* tm = is_v ? &p.tmap_v : &p.tmap_k;
         tma_load_4d(dst, tm, bar, 0, row, hk, b);
-        tma_load_4d(dst + kPanelBytes, tm, bar, 64, row, hk, b);
+        if (is_v || !kQkFp8) tma_load_4d(dst + kPanelBytes, tm, bar, 64, row, hk, b);
       }
       DTB_PROF_FLUSH(24, true);
     }
@@ -371,7 +375,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     setmaxnreg_dec<kRegsService>();
-    constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBlockN, false, false);
+    constexpr uint32_t idesc_qk = kQkFp8 ? make_idesc_e4m3(kBlockM, kBlockN) : make_idesc_bf16(kBlockM, kBlockN, false, false);
     constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, kHeadDim, false, true);
     const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(smem_q), 16, 1024);
     const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem_kv), 16, 1024);
@@ -384,10 +388,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       if (lane == 0) {
         const uint64_t a0 = q_desc0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
         const uint64_t b0 = k_desc0 + static_cast<uint64_t>((slot * kTileBytes) >> 4);
+        if (kQkFp8) {
 #pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-          const uint64_t off = static_cast<uint64_t>(((kk & 3) * 32 + (kk >> 2) * kPanelBytes) >> 4);
-          mma_ss(tmem_base + t * kBlockN, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < kHeadDim / 32; ++kk) {   // 32 one-byte elements = 32 bytes of the swizzled row
+            const uint64_t off = static_cast<uint64_t>((kk * 32) >> 4);
+            mma_ss_f8(tmem_base + t * kBlockN, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+            const uint64_t off = static_cast<uint64_t>(((kk & 3) * 32 + (kk >> 2) * kPanelBytes) >> 4);
+            mma_ss(tmem_base + t * kBlockN, a0 + off, b0 + off, idesc_qk, kk > 0 ? 1u : 0u);
+          }
         }
         mma_commit(smem_u32(&bars->s_full[t]));
       }

@@ -35,15 +35,30 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+namespace {
+int encode_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb, int64_t sh, int64_t ss,
+                int box_rows, int64_t esz);
+}
+
 int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb,
                    int64_t sh, int64_t ss, int box_rows) {
+  return encode_bhsd(out, base, B, H, S, sb, sh, ss, box_rows, 2);
+}
+
+int make_tmap_bhsd_u8(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb, int64_t sh,
+                      int64_t ss, int box_rows) {
+  return encode_bhsd(out, base, B, H, S, sb, sh, ss, box_rows, 1);
+}
+
+namespace {
+int encode_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb, int64_t sh, int64_t ss,
+                int box_rows, int64_t esz) {
   EncodeTiledFn enc = get_encode_tiled();
   if (enc == nullptr) {
     snprintf(g_detail, sizeof(g_detail), "cuTensorMapEncodeTiled entry point not found");
     return DTB_ERR_LAUNCH;
   }
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return DTB_ERR_ALIGN;
-  const int64_t esz = 2;
   if (((ss * esz) & 15) || ((sh * esz) & 15) || ((sb * esz) & 15)) return DTB_ERR_ALIGN;
   if (ss <= 0 || sh < 0 || sb < 0) return DTB_ERR_SHAPE;
   cuuint64_t gdim[4] = {128, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
@@ -55,9 +70,10 @@ int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int
                         static_cast<cuuint64_t>((B > 1 ? sb : H * S * ss) * esz)};
   for (int i = 0; i < 3; ++i)
     if (gstr[i] == 0 || (gstr[i] & 15)) gstr[i] = 256;  // only reachable for size-1 axes
-  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / esz), static_cast<cuuint32_t>(box_rows), 1, 1};   // 128-byte rows
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstr, box, estr,
+  CUresult r = enc(out, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,
+                   const_cast<void*>(base), gdim, gstr, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -67,6 +83,7 @@ int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int
   }
   return DTB_OK;
 }
+}  // namespace
 
 bool device_is_sm100() {
   int dev = 0;

@@ -25,6 +25,10 @@ EncodeTiledFn get_encode_tiled();
 int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb,
                    int64_t sh, int64_t ss, int box_rows);
 
+// Same for an 8-bit (E4M3) [B, H, S, 128] tensor: boxes of 128 bytes x `box_rows`.
+int make_tmap_bhsd_u8(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb, int64_t sh,
+                      int64_t ss, int box_rows);
+
 // Records the CUDA error behind a DTB_ERR_LAUNCH so that dtb_last_error_detail() can name it.
 // Returns true when `e` is cudaSuccess.
 bool cuda_ok(cudaError_t e, const char* what);

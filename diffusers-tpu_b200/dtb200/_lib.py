@@ -20,13 +20,14 @@ STATUS_NAMES = {
 
 FLAG_ZERO_PADDED_ROWS = 0x1
 FLAG_BOUNDED_LOGITS = 0x2
+FLAG_QK_FP8 = 0x8
 STATIC_SCRATCH_BYTES = 32 << 20
 
 # Every symbol the public header declares; tests check that the library exports all of them.
 EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
     "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_attn_fwd_sparse", "dtb_scatter_heads",
-    "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands", "dtb_qk_prepass",
+    "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands", "dtb_qk_prepass", "dtb_quantize_e4m3",
     "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_mma_rate", "dtb_selftest_wait_timeout",
 )
 
@@ -138,6 +139,9 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         lib.dtb_attn_fwd_static_scratch.argtypes = [ctypes.POINTER(AttnParams), vp]
         lib.dtb_attn_fwd_sparse.restype = ctypes.c_int
         lib.dtb_attn_fwd_sparse.argtypes = [ctypes.POINTER(AttnParams), ctypes.POINTER(BlockTable), vp]
+        lib.dtb_quantize_e4m3.restype = ctypes.c_int
+        lib.dtb_quantize_e4m3.argtypes = [vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32,
+                                          ctypes.c_int32, ctypes.c_int32, ctypes.c_float, vp, vp]
         lib.dtb_qk_prepass.restype = ctypes.c_int
         lib.dtb_qk_prepass.argtypes = [ctypes.POINTER(PrepassParams), vp]
         lib.dtb_attn_fwd_scatter.restype = ctypes.c_int

@@ -12,6 +12,7 @@ All compute goes through the C ABI in ``libdtb200_attn.so``; nothing here falls 
 from __future__ import annotations
 
 import ctypes
+import math
 from typing import Optional, Sequence, Tuple, Union
 
 import torch
@@ -145,6 +146,20 @@ def fixed_m_operands(query: torch.Tensor, key: torch.Tensor, *, scale: Optional[
     return mk
 
 
+def quantize_e4m3(x: torch.Tensor, *, mult: float = 1.0) -> torch.Tensor:
+    """Saturating E4M3 cast of a bf16 ``[B, H, S, 128]`` tensor: ``x * mult`` clamped to +-448, as
+    ``diffusers_tpu/kernels/fp8_cast.py:28-39``.  Returns contiguous ``torch.float8_e4m3fn``."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or x.dim() != 4 or x.shape[-1] != 128:
+        raise NotImplementedError("quantize_e4m3 takes CUDA bf16 [B, H, S, 128] tensors")
+    x = _dense_last(x)
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.load().dtb_quantize_e4m3(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2), x.shape[0], x.shape[1],
+                                           x.shape[2], x.shape[3], float(mult), out.data_ptr(), _stream_ptr(x.device))
+    _lib.check(st, "dtb_quantize_e4m3")
+    return out.view(torch.float8_e4m3fn)
+
+
 def attention(
     query: torch.Tensor,
     key: torch.Tensor,
@@ -173,18 +188,28 @@ def attention(
     come back as exact zeros, so padding content cannot reach real rows or leak downstream.
     ``use_fixed_m`` selects the per-head constant-offset softmax for heads whose bound passes the
     gate (``mk`` supplies a precomputed operand, otherwise it is derived from this call's q and k).
+    ``qk_fp8`` casts the pre-scaled query and the key to E4M3 and runs the score MMA in 8-bit floats.
     ``block_*``, ``kv_mask_all`` and ``unroll`` are accepted for signature parity and ignored.
     """
     del block_q, block_kv, block_kv_compute, kv_mask_all, unroll
-    if qk_fp8:
-        raise NotImplementedError("qk_fp8 (E4M3 Q/K) is not built yet")
     _check_inputs(query, key, value)
     query, key, value = _dense_last(query), _dense_last(key), _dense_last(value)
     dev = query.device
+    if qk_fp8:
+        # The reference casts the pre-scaled query and the key to E4M3 in front of the score matmul
+        # (diffusers_tpu/kernels/splash.py:420-424, 607-609); P*V stays bf16.
+        if use_fixed_m and mk is None:
+            raise NotImplementedError("qk_fp8 with use_fixed_m needs a calibrated mk (dtb200.fixed_m.static_fixed_m_operands)")
+        if num_splits > 1:
+            raise NotImplementedError("qk_fp8 has no split-KV variant")
+        s_ = (1.0 / math.sqrt(query.shape[-1])) if scale is None else float(scale)
+        query = quantize_e4m3(query, mult=s_ * LOG2_E)
+        key = quantize_e4m3(key)
+        scale = 1.0 / LOG2_E          # the logits already are in log2 units
     if out is None:
-        out = torch.empty(query.shape, dtype=query.dtype, device=dev)
+        out = torch.empty(query.shape, dtype=value.dtype, device=dev)
     kv_len_t = _kv_len_tensor(kv_len, query.shape[0], dev)
-    flags = 0
+    flags = _lib.FLAG_QK_FP8 if qk_fp8 else 0
     if zero_padded_rows and kv_len_t is not None:
         flags |= _lib.FLAG_ZERO_PADDED_ROWS
     if use_fixed_m:
@@ -194,7 +219,7 @@ def attention(
     else:
         mk = None
     status = _status_buffer(dev)
-    p = _fill_params(query, key, value, out, kv_len_t, mk, scale, flags, num_splits, status)
+    p = _fill_params(query, key, value, out, kv_len_t, mk, scale, flags, 1 if qk_fp8 else num_splits, status)
     lib = _lib.load()
     with torch.cuda.device(dev):
         ws = _workspace(dev, lib.dtb_attn_workspace_bytes(ctypes.byref(p)))

@@ -39,6 +39,7 @@ enum dtb_status {
 /* Flags for dtb_attn_params.flags */
 #define DTB_FLAG_ZERO_PADDED_ROWS 0x1u /* write exact zeros to query rows >= kv_len[b]            */
 #define DTB_FLAG_BOUNDED_LOGITS 0x2u   /* per-head constant softmax offset from `mk` (fixed-m)    */
+#define DTB_FLAG_QK_FP8 0x8u           /* q and k are E4M3 bytes (strides in bytes); dtb_attn_fwd only */
 
 /* One attention call.  All pointers are device pointers unless noted. */
 typedef struct dtb_attn_params {
@@ -189,6 +190,12 @@ int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* stream);
  * (norm_q / norm_k :191-195, apply_rope :251-262, pad zeroing :372-381, swapaxes :388), its torch twin
  * diffusers_tpu/backends/ours_splash_tt.py:189-213, and the operand pass diffusers_tpu/kernels/fixed_m_bound.py:57-118. */
 int dtb_qk_prepass(const dtb_prepass_params* pp, void* stream);
+
+/* Saturating E4M3 cast of a bf16 [B, H, S, 128] tensor, x * mult clamped to +-448, written contiguously; feeds the
+ * DTB_FLAG_QK_FP8 variant of dtb_attn_fwd.  Replaces diffusers_tpu/kernels/fp8_cast.py:28-39 `quantize_saturating` as
+ * applied to q and k in diffusers_tpu/kernels/splash.py:420-424. */
+int dtb_quantize_e4m3(const void* x, int64_t stride_b, int64_t stride_h, int64_t stride_s, int32_t B, int32_t H, int32_t S,
+                      int32_t D, float mult, void* out, void* stream);
 
 /* Hardware self-tests of the descriptor encodings the kernels rely on (one 128x128x128 tile each).
  * They write f32 [128,128] results for the host to compare; no reference counterpart. */

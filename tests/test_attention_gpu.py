@@ -226,8 +226,32 @@ def test_unsupported_inputs_raise_instead_of_falling_back():
     with pytest.raises(NotImplementedError):
         dtb200.attention(y, y, y)
     z = torch.zeros(1, 2, 128, 128, dtype=torch.bfloat16, device=DEV)
-    with pytest.raises(NotImplementedError):
-        dtb200.attention(z, z, z, qk_fp8=True)
+    with pytest.raises(NotImplementedError):           # E4M3 scores with the bounded-logit mode need a calibrated operand
+        dtb200.attention(z, z, z, qk_fp8=True, use_fixed_m=True)
+
+
+@pytest.mark.parametrize("B,H,S,kv_len", [(1, 2, 512, None), (2, 3, 1100, [1100, 777])])
+def test_qk_fp8_variant_matches_oracle_on_quantised_operands(B, H, S, kv_len):
+    from dtb200 import fixed_m as F
+
+    q, k, v = _rand(B, H, S, S, seed=31, gain=1.5)
+    qd, kd = q.to(DEV), k.to(DEV)
+    c = (128 ** -0.5) * F.LOG2_E
+    q8 = dtb200.quantize_e4m3(qd, mult=c)
+    k8 = dtb200.quantize_e4m3(kd)
+    assert q8.dtype == torch.float8_e4m3fn and q8.shape == q.shape
+    # the cast is the saturating round-to-nearest of the reference
+    assert torch.equal(q8.float().cpu(), F.quantize_saturating(q.float() * c).float())
+    assert torch.equal(k8.float().cpu(), F.quantize_saturating(k).float())
+    assert dtb200.quantize_e4m3((qd.float() * 1e4).to(torch.bfloat16)).float().abs().max().item() == 448.0
+    out = dtb200.attention(qd, kd, v.to(DEV), kv_len=kv_len, qk_fp8=True)
+    # oracle on the same quantised operands: the logits are already in log2 units, so softmax scale = ln 2
+    ref = O.attention_fp32(q8.float().cpu(), k8.float().cpu(), v, kv_len=kv_len, scale=1.0 / F.LOG2_E)
+    _check(out, ref, kv_len)
+    # and the variant stays close to the bf16 path: E4M3 keeps 3 mantissa bits of q and k
+    full = O.attention_fp32(q, k, v, kv_len=kv_len)
+    err = (out.float().cpu() - full).abs()
+    assert err.max().item() <= 6e-2 and err.mean().item() <= 6e-3
 
 
 def test_full_size_properties_config2():
