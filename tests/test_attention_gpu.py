@@ -248,10 +248,11 @@ def test_qk_fp8_variant_matches_oracle_on_quantised_operands(B, H, S, kv_len):
     # oracle on the same quantised operands: the logits are already in log2 units, so softmax scale = ln 2
     ref = O.attention_fp32(q8.float().cpu(), k8.float().cpu(), v, kv_len=kv_len, scale=1.0 / F.LOG2_E)
     _check(out, ref, kv_len)
-    # and the variant stays close to the bf16 path: E4M3 keeps 3 mantissa bits of q and k
+    # the variant is lossy by design (E4M3 keeps 3 mantissa bits of q and k): it stays near the full-precision
+    # result but is not held to the bf16 path's tolerance
     full = O.attention_fp32(q, k, v, kv_len=kv_len)
     err = (out.float().cpu() - full).abs()
-    assert err.max().item() <= 6e-2 and err.mean().item() <= 6e-3
+    assert err.max().item() <= 0.25 and err.mean().item() <= 2e-2
 
 
 def test_full_size_properties_config2():
