@@ -39,9 +39,11 @@ def _status_buffer(device: torch.device) -> torch.Tensor:
 
 
 def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
+    """Split-KV scratch, one buffer per (device, stream): calls on different streams may overlap on the GPU."""
     if nbytes == 0:
         return None
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
