@@ -444,9 +444,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int iv = 2 * j + 1;
       const int ik = 2 * j + 2;
-      DTB_PROF_BEGIN();
-      ok = wait_kv(iv);
-      DTB_PROF_END(0);
+      // No wait for V_j or K_{j+1} here: softmax group 0 checks both loads before it publishes P_0(j) (see
+      // there), so the P barriers below already say that the tiles have landed.
       for (int t = 0; t < kQTiles && ok; ++t) {
         DTB_PROF_BEGIN();
         ok = warp_wait(&bars->p_lo[t], j & 1, ctx, SITE_P_FULL + t);
@@ -462,13 +461,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         issue_pv(t, iv % kStages, 1, true);
         if (t == kQTiles - 1) commit_to(&bars->kv_empty[iv % kStages]);
         if (j + 1 < n_tiles) {
-          if (t == 0) {
-            DTB_PROF_BEGIN();
-            ok = wait_kv(ik);
-            DTB_PROF_END(1);
-            if (!ok) break;
-            tc_fence_after();
-          }
           issue_qk(t, ik % kStages);
           if (t == kQTiles - 1) commit_to(&bars->kv_empty[ik % kStages]);
         } else {
@@ -556,8 +548,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     const long long prof_start = clock64();
 #endif
     for (int j = 0; j < n_tiles && ok; ++j) {
+      // The MMA issuer pays ~100 cycles of idle tensor pipe for every barrier it polls, even a satisfied one,
+      // while this group spends a third of every iteration waiting for S.  So one thread of group 0 checks here
+      // that V_j and K_{j+1} have landed (they were requested two tiles ago); its arrival on the P barriers then
+      // carries that fact to the issuer, which uses V_j first in P_0(j) V_j and K_{j+1} first in Q_0 K_{j+1}^T.
+      bool kv_ok = true;
+      if (threadIdx.x == 0) {
+        const int iv = 2 * j + 1, ik = 2 * j + 2;
+        kv_ok = mbar_wait(smem_u32(&bars->kv_full[iv % kStages]), (iv / kStages) & 1, ctx, SITE_KV_FULL + iv % kStages);
+        if (kv_ok && j + 1 < n_tiles)
+          kv_ok = mbar_wait(smem_u32(&bars->kv_full[ik % kStages]), (ik / kStages) & 1, ctx, SITE_KV_FULL + ik % kStages);
+      }
       DTB_PROF_BEGIN();
-      ok = warp_wait(&bars->s_full[t], j & 1, ctx, SITE_S_FULL + t);
+      ok = __all_sync(0xffffffffu, kv_ok && mbar_wait(smem_u32(&bars->s_full[t]), j & 1, ctx, SITE_S_FULL + t));
       DTB_PROF_END(0);
       if (!ok) break;
       tc_fence_after();
