@@ -193,6 +193,17 @@ cudaError_t ensure_kernel_attrs() {
   e = cudaFuncSetAttribute(attn_fwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(kSmemBytes));
   if (e != cudaSuccess) return e;
+  // The register hand-over inside the kernel (setmaxnreg) is sized for kLaunchRegs registers per thread at
+  // launch; with any other count a warpgroup could wait for registers that never come.  Refuse to launch then.
+  const void* variants[3] = {reinterpret_cast<const void*>(attn_fwd_kernel<false, false>),
+                             reinterpret_cast<const void*>(attn_fwd_kernel<true, false>),
+                             reinterpret_cast<const void*>(attn_fwd_kernel<false, true>)};
+  for (const void* fn : variants) {
+    cudaFuncAttributes fa;
+    e = cudaFuncGetAttributes(&fa, fn);
+    if (e != cudaSuccess) return e;
+    if (fa.numRegs != kLaunchRegs) return cudaErrorInvalidConfiguration;
+  }
   if (dev >= 0 && dev < 64) g_attrs_set[dev].store(true, std::memory_order_release);
   return cudaSuccess;
 }
@@ -266,7 +277,7 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
   int st = check_params(p, true);
   if (st != DTB_OK) return st;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
-  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
+  if (!cuda_ok(ensure_kernel_attrs(), "attention kernel attributes (dynamic shared memory size; registers per thread as compiled)")) return DTB_ERR_LAUNCH;
   AttnKernelParams kp;
   st = fill_kernel_params(p, &kp);
   if (st != DTB_OK) return st;
@@ -315,7 +326,7 @@ extern "C" int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_re
   if (r == nullptr || r->o_acc == nullptr || r->m == nullptr || r->l == nullptr) return DTB_ERR_NULL;
   if (reinterpret_cast<uintptr_t>(r->o_acc) & 15u) return DTB_ERR_ALIGN;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
-  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
+  if (!cuda_ok(ensure_kernel_attrs(), "attention kernel attributes (dynamic shared memory size; registers per thread as compiled)")) return DTB_ERR_LAUNCH;
   AttnKernelParams kp;
   st = fill_kernel_params(p, &kp);
   if (st != DTB_OK) return st;
@@ -423,7 +434,7 @@ extern "C" int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* strea
   void* scratch = nullptr;
   st = static_scratch_address(&scratch);
   if (st != DTB_OK) return st;
-  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
+  if (!cuda_ok(ensure_kernel_attrs(), "attention kernel attributes (dynamic shared memory size; registers per thread as compiled)")) return DTB_ERR_LAUNCH;
   AttnKernelParams kp;
   st = fill_kernel_params(p, &kp);
   if (st != DTB_OK) return st;
@@ -472,7 +483,7 @@ extern "C" int dtb_attn_fwd_scatter(const dtb_attn_params* p, const dtb_attn_sca
     if (reinterpret_cast<uintptr_t>(sc->out_ptrs[i]) & 15u) return DTB_ERR_ALIGN;
   }
   if (!device_is_sm100()) return DTB_ERR_ARCH;
-  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
+  if (!cuda_ok(ensure_kernel_attrs(), "attention kernel attributes (dynamic shared memory size; registers per thread as compiled)")) return DTB_ERR_LAUNCH;
   AttnKernelParams kp;
   st = fill_kernel_params(p, &kp);
   if (st != DTB_OK) return st;
@@ -526,7 +537,7 @@ extern "C" int dtb_attn_fwd_sparse(const dtb_attn_params* p, const dtb_block_tab
   if (tb->n_classes < 1 || tb->width < 1 || tb->q_blocks != q_blocks(p)) return DTB_ERR_SHAPE;
   if (tb->n_classes > 1 && tb->head_class == nullptr) return DTB_ERR_NULL;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
-  if (!cuda_ok(ensure_kernel_attrs(), "cudaFuncSetAttribute(max dynamic shared memory)")) return DTB_ERR_LAUNCH;
+  if (!cuda_ok(ensure_kernel_attrs(), "attention kernel attributes (dynamic shared memory size; registers per thread as compiled)")) return DTB_ERR_LAUNCH;
   AttnKernelParams kp;
   st = fill_kernel_params(p, &kp);
   if (st != DTB_OK) return st;

@@ -43,8 +43,18 @@ constexpr int kNumSoftmaxThreads = kQTiles * kBlockM;
 constexpr int kMmaWarp = kNumSoftmaxThreads / 32;
 constexpr int kLoadWarp = kMmaWarp + 1;
 constexpr int kNumThreads = kNumSoftmaxThreads + 128;
-constexpr int kRegsSoftmax = 224;              // 2 * 32 * 224 + 32 * 56 = 16128 <= 16384 per sub-partition
+// Register hand-over between warpgroups.  The kernel is compiled for kLaunchRegs registers per thread (what
+// 384 threads can have at most, rounded down to a multiple of 8; the host side refuses to launch a build
+// whose count differs).  setmaxnreg.dec in the service warpgroup returns registers to a per-CTA pool and
+// setmaxnreg.inc in the two softmax warpgroups takes them from it.  The pool holds nothing else, and an inc
+// that asks for more than the decs released waits for ever - no time-out can end that wait - hence the
+// static_assert.  (Each sub-partition then holds 2 * 32 * 224 + 32 * 56 = 16128 of its 16384 registers.)
+constexpr int kLaunchRegs = 168;
+constexpr int kRegsSoftmax = 224;
 constexpr int kRegsService = 56;
+static_assert((kLaunchRegs - kRegsService) * 128 >= (kRegsSoftmax - kLaunchRegs) * kNumSoftmaxThreads,
+              "setmaxnreg.inc would ask for more registers than setmaxnreg.dec releases");
+static_assert(kNumThreads * kLaunchRegs <= 65536, "the CTA does not fit the register file");
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units: rescale O only when the row max grew by > 2^8
 constexpr float kFixedMRecenter = 88.0f;     // bounded-logit mode exponent offset (m - 88)
