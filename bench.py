@@ -42,7 +42,7 @@ UNIT = "TFLOP/s"
 LAYERS = {"c1_image512_cpu": 60, "c2_image1024": 60, "c3_image2048": 20, "c4_video480p": 4, "c5_video768p": 1}
 # DRAM bytes per launch of attn_fwd_kernel on the c2 workload (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the ncu capture summarised in profiles/attn_fwd_kernel_c2_image1024.md (algorithmic bytes: 226 MB).
-NCU_TRAFFIC_BYTES_C2 = 200_563_456
+NCU_TRAFFIC_BYTES_C2 = 199_908_864
 
 
 def measured_peaks():
