@@ -119,25 +119,14 @@ __device__ __forceinline__ void report_error(const AbortCtx& ctx, int code, int 
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int site,
                                           uint64_t budget_ns = kWaitBudgetNs) {
-  // The clock is first read after 64 unsuccessful polls (each of which the hardware may already have
-  // suspended for a while): a wait that is satisfied soon - the common case, and on the critical path of
-  // every hand-off between the softmax warps and the MMA issuer - never pays for a timer read.
-#ifdef DTB_WAIT_SPIN
-#define DTB_POLL mbar_test_wait
-#else
-#define DTB_POLL mbar_try_wait
-#endif
-  if (DTB_POLL(bar, parity)) return true;
-  uint64_t t0 = 0;
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
-    if (DTB_POLL(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3f) == 0) {
       if (*ctx.cta_abort) return false;
-      const uint64_t now = globaltimer_ns();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > budget_ns) {
+      if (globaltimer_ns() - t0 > budget_ns) {
         report_error(ctx, DEV_ERR_WAIT_TIMEOUT, site, static_cast<int>(parity));
         return false;
       }
