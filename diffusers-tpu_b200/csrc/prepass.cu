@@ -34,6 +34,9 @@ struct PrepassParams {
 // step and the block writes 2 KB of contiguous [B, H, S, D] output per head, and the rotary table row of the
 // position is loaded once per warp and reused for every head.  Per-head norm maxima are kept in shared memory
 // and flushed once per block.
+#ifndef DTB_PREPASS_BLOCKS
+#define DTB_PREPASS_BLOCKS 4
+#endif
 constexpr int kTilePositions = 8;
 constexpr int kAccessesInFlight = 4;   // 16-byte loads outstanding per lane (two rows each per warp)
 
@@ -53,9 +56,11 @@ __device__ __forceinline__ float half_warp_sum(float v) {
   return v;
 }
 
-__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16(v)); }
+// The two halves of a bf16 pair as f32 (exact).
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
-__global__ void __launch_bounds__(256) qk_prepass_kernel(const __grid_constant__ PrepassParams p) {
+__global__ void __launch_bounds__(256, DTB_PREPASS_BLOCKS) qk_prepass_kernel(const __grid_constant__ PrepassParams p) {
   extern __shared__ int head_max[];                   // [H] row-norm maxima (as int bits) of this block
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -84,23 +89,21 @@ __global__ void __launch_bounds__(256) qk_prepass_kernel(const __grid_constant__
     const int s = static_cast<int>(tile % s_tiles) * kTilePositions + warp;
     if (s >= p.S) continue;                           // warp-uniform
     const bool live = p.kv_len == nullptr || s < p.kv_len[b];
-    float cs[8], sn[8];
+    // cos / sin of this lane's eight channels as bf16 pairs (the tables are used in the input dtype, as the
+    // reference casts them); lanes outside the rotated channels keep cos = 1, sin = 0
+    uint32_t cs2[4], sn2[4];
     if (which < 2 && p.cos != nullptr && (first || second)) {
-      // tables are used in the input dtype, as the reference casts them
       const float4* cp = reinterpret_cast<const float4*>(p.cos + static_cast<int64_t>(s) * p.rotary) + 2 * hl;
       const float4* sp = reinterpret_cast<const float4*>(p.sin + static_cast<int64_t>(s) * p.rotary) + 2 * hl;
       const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
-      cs[0] = round_bf16(c0.x); cs[1] = round_bf16(c0.y); cs[2] = round_bf16(c0.z); cs[3] = round_bf16(c0.w);
-      cs[4] = round_bf16(c1.x); cs[5] = round_bf16(c1.y); cs[6] = round_bf16(c1.z); cs[7] = round_bf16(c1.w);
-      sn[0] = round_bf16(s0.x); sn[1] = round_bf16(s0.y); sn[2] = round_bf16(s0.z); sn[3] = round_bf16(s0.w);
-      sn[4] = round_bf16(s1.x); sn[5] = round_bf16(s1.y); sn[6] = round_bf16(s1.z); sn[7] = round_bf16(s1.w);
-      if (first) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sn[i] = -sn[i];   // turned = (-second half, first half)
-      }
+      const float sg = first ? -1.0f : 1.0f;   // turned = (-second half, first half)
+      cs2[0] = pack_bf16x2(c0.x, c0.y); cs2[1] = pack_bf16x2(c0.z, c0.w);
+      cs2[2] = pack_bf16x2(c1.x, c1.y); cs2[3] = pack_bf16x2(c1.z, c1.w);
+      sn2[0] = pack_bf16x2(sg * s0.x, sg * s0.y); sn2[1] = pack_bf16x2(sg * s0.z, sg * s0.w);
+      sn2[2] = pack_bf16x2(sg * s1.x, sg * s1.y); sn2[3] = pack_bf16x2(sg * s1.z, sg * s1.w);
     } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { cs[i] = 1.f; sn[i] = 0.f; }
+      for (int i = 0; i < 4; ++i) { cs2[i] = 0x3f803f80u; sn2[i] = 0u; }
     }
     const __nv_bfloat16* in_row = p.in[which] + b * p.sb[which] + s * p.ss[which];
     __nv_bfloat16* out_row = p.out[which] + (static_cast<int64_t>(b) * p.H * p.S + s) * kD;
@@ -124,22 +127,23 @@ __global__ void __launch_bounds__(256) qk_prepass_kernel(const __grid_constant__
           for (int i = 0; i < 8; ++i) ssq += x[i] * x[i];
           ssq = half_warp_sum(ssq);
           const float rrms = rsqrtf(ssq * (1.0f / kD) + p.eps);
-          float y[8];
+          // normalised values, rounded to bf16 as the reference's RMSNorm returns them, kept as bf16 pairs
+          uint32_t yp[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i)   // normalised value, rounded to bf16 as the reference's RMSNorm returns it
-            y[i] = round_bf16(x[i] * rrms * wgt[i]);
+          for (int i = 0; i < 4; ++i)
+            yp[i] = pack_bf16x2(x[2 * i] * rrms * wgt[2 * i], x[2 * i + 1] * rrms * wgt[2 * i + 1]);
           if (p.cos != nullptr) {
-            // channel c < rotary/2 pairs with c + rotary/2: out = y*cos + turned*sin
+            // channel c < rotary/2 pairs with c + rotary/2: out = y*cos + turned*sin; the partner's values
+            // travel as the bf16 pairs they already are
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float other = __shfl_sync(0xffffffffu, y[i], partner);
-              y[i] = y[i] * cs[i] + other * sn[i];
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t op = __shfl_sync(0xffffffffu, yp[i], partner);
+              const float y0 = bf16_lo(yp[i]) * bf16_lo(cs2[i]) + bf16_lo(op) * bf16_lo(sn2[i]);
+              const float y1 = bf16_hi(yp[i]) * bf16_hi(cs2[i]) + bf16_hi(op) * bf16_hi(sn2[i]);
+              yp[i] = pack_bf16x2(y0, y1);
             }
           }
-          packed.x = pack_bf16x2(y[0], y[1]);
-          packed.y = pack_bf16x2(y[2], y[3]);
-          packed.z = pack_bf16x2(y[4], y[5]);
-          packed.w = pack_bf16x2(y[6], y[7]);
+          packed = make_uint4(yp[0], yp[1], yp[2], yp[3]);
           if (!live) packed = make_uint4(0u, 0u, 0u, 0u);
           if (want_norms) {
             float z[8];
