@@ -459,16 +459,6 @@ extern "C" int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* strea
   return launch_ok("combine_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
 
-#ifdef DTB_PROFILE_WAITS
-// Diagnostic builds only: copies out and clears the wait-time counters (32 x uint64).
-extern "C" int dtb_debug_read_wait_profile(unsigned long long* out) {
-  if (cudaMemcpyFromSymbol(out, dtb::g_wait_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return DTB_ERR_LAUNCH;
-  unsigned long long zeros[32] = {};
-  if (cudaMemcpyToSymbol(dtb::g_wait_prof, zeros, sizeof(zeros)) != cudaSuccess) return DTB_ERR_LAUNCH;
-  return DTB_OK;
-}
-#endif
-
 extern "C" int dtb_attn_fwd_scatter(const dtb_attn_params* p, const dtb_attn_scatter* sc, void* stream) {
   int st = check_params(p, false);
   if (st != DTB_OK) return st;

@@ -58,30 +58,6 @@ static_assert(kNumThreads * kLaunchRegs <= 65536, "the CTA does not fit the regi
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;    // log2 units: rescale O only when the row max grew by > 2^8
 constexpr float kFixedMRecenter = 88.0f;     // bounded-logit mode exponent offset (m - 88)
-// Of every four consecutive key pairs, this many take the FMA-pipe polynomial exp2 instead of the
-// MUFU unit, which otherwise is as busy as the tensor core (one ex2 per score).
-#ifndef DTB_EXP2_POLY_QUARTERS
-#define DTB_EXP2_POLY_QUARTERS 0
-#endif
-constexpr int kExp2PolyQuarters = DTB_EXP2_POLY_QUARTERS;
-
-// Optional wait-time accounting (a diagnostic build, -DDTB_PROFILE_WAITS): cycles spent in each kind of
-// barrier wait, summed over CTAs, readable through dtb_debug_read_wait_profile().
-#ifdef DTB_PROFILE_WAITS
-__device__ unsigned long long g_wait_prof[32];
-#define DTB_PROF_DECL long long prof_t = 0; long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define DTB_PROF_BEGIN() prof_t = clock64()
-#define DTB_PROF_END(slot) prof_acc[slot] += clock64() - prof_t
-#define DTB_PROF_FLUSH(base, cond)                                                         \
-  if (cond) {                                                                              \
-    for (int i_ = 0; i_ < 8; ++i_) atomicAdd(&g_wait_prof[(base) + i_], (unsigned long long)prof_acc[i_]); \
-  }
-#else
-#define DTB_PROF_DECL
-#define DTB_PROF_BEGIN()
-#define DTB_PROF_END(slot)
-#define DTB_PROF_FLUSH(base, cond)
-#endif
 
 struct __align__(8) PipelineBarriers {
   uint64_t q_full[kQTiles];
@@ -152,21 +128,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
                                              bool o_live, float& m_used, float& l_sum, uint32_t bar_p_lo,
                                              uint32_t bar_p_hi) {
   uint32_t sr[kBlockN];
-#ifdef DTB_PROFILE_WAITS
-  const bool prof_on = (threadIdx.x & 127) == 0;
-  const int prof_base = 8 + 8 * (threadIdx.x >> 7);
-  long long pt = clock64();
-#define DTB_PROF_LAP(slot)                                                              \
-  {                                                                                     \
-    const long long now_ = clock64();                                                   \
-    if (prof_on) atomicAdd(&g_wait_prof[prof_base + (slot)], (unsigned long long)(now_ - pt)); \
-    pt = clock64();                                                                     \
-  }
-#else
-#define DTB_PROF_LAP(slot)
-#endif
   tmem_ld128_sync(s_tmem, sr);
-  DTB_PROF_LAP(2);
   if (valid_cols < kBlockN) {
 #pragma unroll
     for (int i = 0; i < kBlockN; ++i)
@@ -215,12 +177,8 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
       const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sr[col]), __uint_as_float(sr[col + 1])), scale2, neg_m2);
       float x0, x1, p0, p1;
       unpack_f32x2(x2, x0, x1);
-      if ((i & 3) < kExp2PolyQuarters) {
-        ex2_poly_f32x2(pack_f32x2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f)), p0, p1);
-      } else {
-        p0 = ex2(x0);
-        p1 = ex2(x1);
-      }
+      p0 = ex2(x0);
+      p1 = ex2(x1);
       acc2 = add_f32x2(acc2, pack_f32x2(p0, p1));
       pk[i] = pack_bf16x2(p0, p1);
     }
@@ -228,7 +186,6 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
     tmem_wait_st();
     tc_fence_before();
     mbar_arrive(half == 0 ? bar_p_lo : bar_p_hi);
-    DTB_PROF_LAP(4 + half);
   }
   float a0, a1;
   unpack_f32x2(acc2, a0, a1);
@@ -353,7 +310,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     // ------------------------------------------------------------------ TMA producer
     setmaxnreg_dec<kRegsService>();
     bool ok = true;
-    DTB_PROF_DECL;
     if (lane == 0) {
       for (int t = 0; t < kQTiles; ++t) {
         const uint32_t bar = smem_u32(&bars->q_full[t]);
@@ -365,9 +321,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       for (int i = 0; i < 2 * n_tiles && ok; ++i) {
         const int slot = i % kStages;
         const int use = i / kStages;
-        DTB_PROF_BEGIN();
         if (use > 0) ok = mbar_wait(smem_u32(&bars->kv_empty[slot]), (use - 1) & 1, ctx, SITE_KV_EMPTY + slot);
-        DTB_PROF_END(0);
         if (!ok) break;
         const uint32_t bar = smem_u32(&bars->kv_full[slot]);
         const bool is_v = (i & 1) != 0;
@@ -379,7 +333,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         tma_load_4d(dst, tm, bar, 0, row, hk, b);
         if (is_v || !kQkFp8) tma_load_4d(dst + kPanelBytes, tm, bar, 64, row, hk, b);
       }
-      DTB_PROF_FLUSH(24, true);
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
@@ -391,8 +344,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem_kv), 16, 1024);
     const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem_kv), kPanelBytes, 1024);
     bool ok = true;
-    DTB_PROF_DECL;
-    const long long prof_start = clock64();
 
     auto issue_qk = [&](int t, int slot) {
       if (lane == 0) {
@@ -457,15 +408,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       // No wait for V_j or K_{j+1} here: softmax group 0 checks both loads before it publishes P_0(j) (see
       // there), so the P barriers below already say that the tiles have landed.
       for (int t = 0; t < kQTiles && ok; ++t) {
-        DTB_PROF_BEGIN();
         ok = warp_wait(&bars->p_lo[t], j & 1, ctx, SITE_P_FULL + t);
-        DTB_PROF_END(2 + t);
         if (!ok) break;
         tc_fence_after();
         issue_pv(t, iv % kStages, 0, j > 0 || o_preloaded);
-        DTB_PROF_BEGIN();
         ok = warp_wait(&bars->p_hi[t], j & 1, ctx, SITE_P_HI + t);
-        DTB_PROF_END(4 + t);
         if (!ok) break;
         tc_fence_after();
         issue_pv(t, iv % kStages, 1, true);
@@ -478,11 +425,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         }
       }
     }
-#ifdef DTB_PROFILE_WAITS
-    prof_acc[6] = clock64() - prof_start;
-    prof_acc[7] = n_tiles;
-#endif
-    DTB_PROF_FLUSH(0, lane == 0);
   } else if (warp < kMmaWarp) {
     // ------------------------------------------------------------------ softmax groups
     setmaxnreg_inc<kRegsSoftmax>();
@@ -553,10 +495,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     }
 
     bool ok = true;
-    DTB_PROF_DECL;
-#ifdef DTB_PROFILE_WAITS
-    const long long prof_start = clock64();
-#endif
     for (int j = 0; j < n_tiles && ok; ++j) {
       // The MMA issuer pays ~100 cycles of idle tensor pipe for every barrier it polls, even a satisfied one,
       // while this group spends a third of every iteration waiting for S.  So one thread of group 0 checks here
@@ -569,9 +507,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
         if (kv_ok && j + 1 < n_tiles)
           kv_ok = mbar_wait(smem_u32(&bars->kv_full[ik % kStages]), (ik / kStages) & 1, ctx, SITE_KV_FULL + ik % kStages);
       }
-      DTB_PROF_BEGIN();
       ok = __all_sync(0xffffffffu, kv_ok && mbar_wait(smem_u32(&bars->s_full[t]), j & 1, ctx, SITE_S_FULL + t));
-      DTB_PROF_END(0);
       if (!ok) break;
       tc_fence_after();
       const int tile = tile_list != nullptr ? tile_list[tile_begin + j] : tile_begin + j;
@@ -583,13 +519,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
       }
       o_live = true;
     }
-    DTB_PROF_BEGIN();
     if (ok) ok = warp_wait(&bars->o_full[t], 0, ctx, SITE_O_FULL + t);
-    DTB_PROF_END(1);
-#ifdef DTB_PROFILE_WAITS
-    prof_acc[6] = clock64() - prof_start;
-#endif
-    DTB_PROF_FLUSH(8 + 8 * t, (threadIdx.x & 127) == 0);
     if (ok) {
       tc_fence_after();
       if (kResidual) {

@@ -28,7 +28,7 @@ EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
     "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_attn_fwd_sparse", "dtb_scatter_heads",
     "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands", "dtb_qk_prepass", "dtb_quantize_e4m3",
-    "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_mma_rate", "dtb_selftest_wait_timeout",
+    "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_wait_timeout",
 )
 
 
@@ -162,8 +162,6 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.restype = ctypes.c_int
             fn.argtypes = [vp, vp, vp, i32p, vp]
-        lib.dtb_selftest_mma_rate.restype = ctypes.c_int
-        lib.dtb_selftest_mma_rate.argtypes = [ctypes.c_int, ctypes.c_int, vp, i32p, vp]
         lib.dtb_selftest_wait_timeout.restype = ctypes.c_int
         lib.dtb_selftest_wait_timeout.argtypes = [ctypes.c_ulonglong, ctypes.c_int, i32p, i32p, vp]
         _lib = lib

@@ -205,23 +205,6 @@ int dtb_selftest_pv(const void* p, const void* v, float* o_out, int32_t* status,
 /* Bounded-wait probe: one warp waits on a barrier that is never signalled; after budget_ns (<= 2 s) the wait gives up,
  * writes {1 (timeout), site, CTA, parity} to `status` (4 x int32, zeroed by the caller) and 2 to *returned. */
 int dtb_selftest_wait_timeout(unsigned long long budget_ns, int site, int32_t* status, int32_t* returned, void* stream);
-/* Tensor-pipe rate probe on one SM: `iters` rounds of eight back-to-back 16-deep MMAs.  mode 0: both operands
- * in shared memory, N = 128; 1: N = 64; 2: A operand in tensor memory, N = 128; 3: N = 256; 4: as 0 with the
- * accumulator alternating every instruction; 5: as 0 with two issuing threads in different warps (cycles are for
- * both streams together); 6: shared-memory-A and tensor-memory-A instructions interleaved one by one.
- * Modes 0-6 choose the stream inside the issue loop at run time, which by itself slows the loop (99-143 cycles
- * per instruction); the issue-path probe, mode = 100 + 20 * style + stream (+ 1000 * g for a parameter of 16 * g),
- * compiles one loop per stream and reaches the pipe rate (64 cycles per 128x128x16 instruction, 128 at N = 256).
- * style 0/1: one thread in a divergent branch; 2/3: the whole warp computes the operands and lane 0's instruction
- * is predicated (odd styles take the tensor-memory base as the constant 0).  stream 0-3 as modes 0-3; 4 = mode 4;
- * 5: arrive + satisfied wait + fence on an mbarrier between blocks of four instructions; 6: the thread idles 16 * g
- * cycles between blocks; 7: fence only; 8: satisfied wait only; 9: wait + fence; 10: poll issued a block early;
- * 11: a shared-memory load and test; 12: tcgen05.commit; 13: other warps load/store tensor memory; 14/15: operand
- * descriptors that change per block (64-bit / low words); 16: other warps store to shared memory every 16 * g
- * cycles; 17/18: two arithmetic warps on the issuer's / another sub-partition (g picks the mix: 0 FMA+ex2, 1 FMA,
- * 2 ex2, 3 integer, 4 sleeping); 19: 15 with the warps of 17.
- * out_cycles (device, 3 x int64): cycles spent issuing, cycles until completion, 1 if completed. */
-int dtb_selftest_mma_rate(int mode, int iters, long long* out_cycles, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -95,18 +95,3 @@ def test_python_api_refuses_cpu_tensors():
         dtb200.attention(q, q, q)
     with pytest.raises(ValueError, match="use_fixed_m needs"):
         dtb200.residual_attention(q, q, q, use_fixed_m=True)
-
-
-def test_rate_probe_rejects_bad_requests_before_touching_a_device():
-    """Null output, negative modes and iteration counts outside 1..100000 are shape errors whatever the
-    device; a well-formed request on a machine without an sm_100 GPU is an architecture error, not a launch."""
-    import torch
-
-    lib = _lib.load()
-    buf = (ctypes.c_longlong * 3)()
-    assert lib.dtb_selftest_mma_rate(0, 10, None, None, None) == 1          # DTB_ERR_NULL
-    for mode, iters in ((-1, 10), (0, 0), (0, 100001), (114, -5)):
-        assert lib.dtb_selftest_mma_rate(mode, iters, buf, None, None) == 3   # DTB_ERR_SHAPE
-    if not torch.cuda.is_available():
-        for mode in (0, 6, 100, 179, 16117):
-            assert lib.dtb_selftest_mma_rate(mode, 10, buf, None, None) == 5  # DTB_ERR_ARCH

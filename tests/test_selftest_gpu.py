@@ -59,41 +59,3 @@ def test_bounded_wait_gives_up_and_reports():
     y = torch.zeros_like(x)
     _run(lib.dtb_selftest_tmem_roundtrip, x, y)
     assert torch.equal(x, y)
-
-
-def test_mma_rate_probe_completes():
-    lib = _lib.load()
-    out = torch.zeros(3, dtype=torch.int64, device="cuda")
-    status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    for mode in range(7):
-        _lib.check(lib.dtb_selftest_mma_rate(mode, 100, out.data_ptr(), status.data_ptr(), None), "dtb_selftest_mma_rate")
-        torch.cuda.synchronize()
-        issue, total, ok = out.tolist()
-        assert ok == 1 and 0 < total < 100 * 8 * 400      # well under 400 cycles per 16-deep MMA
-    assert status.tolist() == [0, 0, 0, 0]
-
-
-def test_mma_issue_probe_reaches_the_pipe_rate():
-    """One thread issuing back-to-back 128x128x16 MMAs keeps the pipe at 64 cycles per instruction, whichever way
-    the loop is written and whether or not the operands move; idling the thread between blocks costs pipe time."""
-    lib = _lib.load()
-    out = torch.zeros(3, dtype=torch.int64, device="cuda")
-    status = torch.zeros(4, dtype=torch.int32, device="cuda")
-
-    def cycles_per_mma(mode, iters=500):
-        out.zero_()
-        _lib.check(lib.dtb_selftest_mma_rate(mode, iters, out.data_ptr(), status.data_ptr(), None), "dtb_selftest_mma_rate")
-        torch.cuda.synchronize()
-        _, total, ok = out.tolist()
-        assert ok == 1
-        return total / iters / 8
-
-    for style in range(4):
-        for stream in (0, 2, 14, 15):           # SS N=128, TS N=128, moving operands (64-bit / low words)
-            assert 60 < cycles_per_mma(100 + 20 * style + stream) < 100
-    plain = cycles_per_mma(100 + 2)
-    gapped = cycles_per_mma(1000 * (256 // 16) + 100 + 6)      # 256 idle cycles between blocks of four
-    assert gapped > plain + 40                                  # ~64 more per instruction: nothing covers the gap
-    for stream in (5, 8, 12, 13, 16, 17, 18, 19):               # the other between-block and contention variants run
-        assert 60 < cycles_per_mma(100 + stream) < 200
-    assert status.tolist() == [0, 0, 0, 0]
