@@ -144,6 +144,11 @@ int check_params(const dtb_attn_params* p, bool need_o) {
   if (p->B <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->Sq <= 0 || p->Skv <= 0) return DTB_ERR_SHAPE;
   if (p->Hq % p->Hkv != 0) return DTB_ERR_SHAPE;
   if (p->Hq > 65535 || static_cast<int64_t>(p->B) * 64 > 65535) return DTB_ERR_SHAPE;
+  // an axis of extent > 1 must have a positive stride (no broadcast or reversed views)
+  if (p->q_stride_s <= 0 || p->k_stride_s <= 0 || p->v_stride_s <= 0) return DTB_ERR_SHAPE;
+  if (p->Hq > 1 && p->q_stride_h <= 0) return DTB_ERR_SHAPE;
+  if (p->Hkv > 1 && (p->k_stride_h <= 0 || p->v_stride_h <= 0)) return DTB_ERR_SHAPE;
+  if (p->B > 1 && (p->q_stride_b <= 0 || p->k_stride_b <= 0 || p->v_stride_b <= 0)) return DTB_ERR_SHAPE;
   if (need_o) {
     if (reinterpret_cast<uintptr_t>(p->o) & 15u) return DTB_ERR_ALIGN;
     if ((p->o_stride_s * 2) & 15 || (p->o_stride_h * 2) & 15 || (p->o_stride_b * 2) & 15) return DTB_ERR_ALIGN;
@@ -286,6 +291,7 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
   int splits = resolve_splits(p);
   if (splits > 1) {
     const size_t need = split_workspace_bytes(p, splits);
+    if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u)) return DTB_ERR_ALIGN;
     if (workspace == nullptr || workspace_bytes < need) {
       if (p->num_splits > 1) return DTB_ERR_WORKSPACE;  // explicitly requested: refuse
       splits = 1;                                       // automatic: run unsplit
@@ -346,6 +352,7 @@ extern "C" int dtb_attn_finalize(const dtb_attn_params* p, const dtb_attn_residu
   if (p == nullptr || p->o == nullptr || r == nullptr || r->o_acc == nullptr || r->m == nullptr || r->l == nullptr)
     return DTB_ERR_NULL;
   if (p->D != kHeadDim || p->B <= 0 || p->Hq <= 0 || p->Sq <= 0) return DTB_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(r->o_acc) & 15u) return DTB_ERR_ALIGN;
   if ((reinterpret_cast<uintptr_t>(p->o) & 7u) || (p->o_stride_s & 3) || (p->o_stride_h & 3) || (p->o_stride_b & 3))
     return DTB_ERR_ALIGN;
   const int64_t out_rows = static_cast<int64_t>(p->B) * p->Hq * p->Sq;
@@ -361,6 +368,10 @@ extern "C" int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float*
   if (p->flags & DTB_FLAG_QK_FP8) return DTB_ERR_UNSUPPORTED;
   if (norms == nullptr || mk_out == nullptr) return DTB_ERR_NULL;
   if ((reinterpret_cast<uintptr_t>(p->q) & 7u) || (reinterpret_cast<uintptr_t>(p->k) & 7u)) return DTB_ERR_ALIGN;
+  // rows are read 8 bytes per lane: every row must start on an 8-byte boundary
+  if ((p->q_stride_s & 3) || (p->k_stride_s & 3) || (p->Hq > 1 && (p->q_stride_h & 3)) || (p->Hkv > 1 && (p->k_stride_h & 3)) ||
+      (p->B > 1 && ((p->q_stride_b & 3) || (p->k_stride_b & 3))))
+    return DTB_ERR_ALIGN;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (!cuda_ok(cudaMemsetAsync(norms, 0, sizeof(float) * (p->Hq + p->Hkv), s), "cudaMemsetAsync")) return DTB_ERR_LAUNCH;
   const float scale = p->scale > 0.f ? p->scale : 1.0f / sqrtf(static_cast<float>(p->D));

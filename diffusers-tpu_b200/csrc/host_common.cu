@@ -59,8 +59,10 @@ int encode_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_
     return DTB_ERR_LAUNCH;
   }
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return DTB_ERR_ALIGN;
-  if (((ss * esz) & 15) || ((sh * esz) & 15) || ((sb * esz) & 15)) return DTB_ERR_ALIGN;
-  if (ss <= 0 || sh < 0 || sb < 0) return DTB_ERR_SHAPE;
+  if (((ss * esz) & 15) || (H > 1 && ((sh * esz) & 15)) || (B > 1 && ((sb * esz) & 15))) return DTB_ERR_ALIGN;
+  // An axis of extent > 1 needs a positive stride: a broadcast (stride 0) or reversed view cannot be described
+  // to TMA, and substituting a stride would read the wrong memory.
+  if (ss <= 0 || (H > 1 && sh <= 0) || (B > 1 && sb <= 0)) return DTB_ERR_SHAPE;
   cuuint64_t gdim[4] = {128, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
                         static_cast<cuuint64_t>(B)};
   // A size-1 axis may come with any stride (torch reports arbitrary values there);
@@ -68,8 +70,8 @@ int encode_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_
   cuuint64_t gstr[3] = {static_cast<cuuint64_t>(ss * esz),
                         static_cast<cuuint64_t>((H > 1 ? sh : S * ss) * esz),
                         static_cast<cuuint64_t>((B > 1 ? sb : H * S * ss) * esz)};
-  for (int i = 0; i < 3; ++i)
-    if (gstr[i] == 0 || (gstr[i] & 15)) gstr[i] = 256;  // only reachable for size-1 axes
+  if (H == 1 && (gstr[1] == 0 || (gstr[1] & 15))) gstr[1] = 256;
+  if (B == 1 && (gstr[2] == 0 || (gstr[2] & 15))) gstr[2] = 256;
   cuuint32_t box[4] = {static_cast<cuuint32_t>(128 / esz), static_cast<cuuint32_t>(box_rows), 1, 1};   // 128-byte rows
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(out, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 4,

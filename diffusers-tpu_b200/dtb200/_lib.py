@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
     "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_attn_fwd_sparse", "dtb_scatter_heads",
     "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands", "dtb_qk_prepass", "dtb_quantize_e4m3",
+    "dtb_smooth_k", "dtb_smooth_k_scratch_bytes", "dtb_fixed_m_from_norms",
     "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_wait_timeout",
 )
 
@@ -104,6 +105,20 @@ class PrepassParams(ctypes.Structure):
     ]
 
 
+class SmoothKParams(ctypes.Structure):
+    """Mirror of ``dtb_smooth_k_params``."""
+
+    _fields_ = [
+        ("k", ctypes.c_void_p),
+        ("k_stride_b", ctypes.c_int64), ("k_stride_h", ctypes.c_int64), ("k_stride_s", ctypes.c_int64),
+        ("out", ctypes.c_void_p),
+        ("out_stride_b", ctypes.c_int64), ("out_stride_h", ctypes.c_int64), ("out_stride_s", ctypes.c_int64),
+        ("kv_len", ctypes.c_void_p), ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+        ("k_norm_max", ctypes.c_void_p),
+        ("B", ctypes.c_int32), ("H", ctypes.c_int32), ("S", ctypes.c_int32), ("D", ctypes.c_int32),
+    ]
+
+
 _lock = threading.Lock()
 _lib = None
 
@@ -142,6 +157,12 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         lib.dtb_quantize_e4m3.restype = ctypes.c_int
         lib.dtb_quantize_e4m3.argtypes = [vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32,
                                           ctypes.c_int32, ctypes.c_int32, ctypes.c_float, vp, vp]
+        lib.dtb_smooth_k.restype = ctypes.c_int
+        lib.dtb_smooth_k.argtypes = [ctypes.POINTER(SmoothKParams), vp]
+        lib.dtb_smooth_k_scratch_bytes.restype = ctypes.c_size_t
+        lib.dtb_smooth_k_scratch_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32]
+        lib.dtb_fixed_m_from_norms.restype = ctypes.c_int
+        lib.dtb_fixed_m_from_norms.argtypes = [vp, vp, ctypes.c_int32, ctypes.c_int32, ctypes.c_float, vp, vp]
         lib.dtb_qk_prepass.restype = ctypes.c_int
         lib.dtb_qk_prepass.argtypes = [ctypes.POINTER(PrepassParams), vp]
         lib.dtb_attn_fwd_scatter.restype = ctypes.c_int

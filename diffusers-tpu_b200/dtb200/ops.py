@@ -84,8 +84,9 @@ def _check_inputs(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor) -
 
 def _dense_last(t: torch.Tensor) -> torch.Tensor:
     """Returns ``t`` if the kernel can address it in place (contiguous head_dim, 16-byte strides)."""
-    ok = t.stride(-1) == 1 and all((s * 2) % 16 == 0 for s in t.stride()[:-1]) and t.data_ptr() % 16 == 0
-    return t if ok else t.contiguous()
+    ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(
+        n == 1 or (s > 0 and (s * 2) % 16 == 0) for n, s in zip(t.shape[:-1], t.stride()[:-1]))
+    return t if ok else t.contiguous()   # broadcast (stride 0) and odd-stride views are materialised
 
 
 def _kv_len_tensor(kv_len: KvLen, batch: int, device: torch.device) -> Optional[torch.Tensor]:
@@ -162,6 +163,49 @@ def quantize_e4m3(x: torch.Tensor, *, mult: float = 1.0) -> torch.Tensor:
     return out.view(torch.float8_e4m3fn)
 
 
+def _smooth_k(key: torch.Tensor, *, kv_len: KvLen = None, out: Optional[torch.Tensor] = None,
+              want_norms: bool = False):
+    """k-smoothing: ``key - mean_seq(key)`` over the valid rows of each (batch, head), padded rows zeroed.
+
+    The caller-side preconditioning of ``diffusers_tpu/kernels/mesh_attention.py:234-237`` (unpadded) and
+    ``diffusers_tpu/models/minimax_h3/jax_server.py:276-281`` (padded: f32 sum over the kept rows divided by
+    ``kv_len``, mean rounded to the key dtype, pads written as zeros).  Softmax is invariant to it; it makes
+    every query row's largest logit non-negative, which the bounded-logit softmax's wide gate presumes.
+    ``out`` may be ``key`` (in place).  With ``want_norms`` also returns the ``[H]`` f32 largest output row
+    norm per head.
+    """
+    if not key.is_cuda:
+        raise RuntimeError("key must be a CUDA tensor: dtb200 has no CPU path")
+    if key.dtype != torch.bfloat16 or key.dim() != 4 or key.shape[-1] != 128:
+        raise NotImplementedError(f"smooth_k takes bf16 [B, H, S, 128] tensors, got {key.dtype} {tuple(key.shape)}")
+    if key.stride(-1) != 1 or key.data_ptr() % 16 or any(st % 8 for st in key.stride()[:3]):
+        key = key.contiguous()
+    B, H, S, _ = key.shape
+    dev = key.device
+    if out is None:
+        out = torch.empty((B, H, S, 128), dtype=torch.bfloat16, device=dev)
+    lib = _lib.load()
+    scratch = torch.empty(lib.dtb_smooth_k_scratch_bytes(B, H), dtype=torch.uint8, device=dev)
+    norms = torch.empty(H, dtype=torch.float32, device=dev) if want_norms else None
+    kv_len_t = _kv_len_tensor(kv_len, B, dev)
+    sp = _lib.SmoothKParams()
+    sp.k = key.data_ptr()
+    sp.k_stride_b, sp.k_stride_h, sp.k_stride_s = key.stride()[:3]
+    sp.out = out.data_ptr()
+    sp.out_stride_b, sp.out_stride_h, sp.out_stride_s = out.stride()[:3]
+    sp.kv_len = kv_len_t.data_ptr() if kv_len_t is not None else None
+    sp.scratch, sp.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    sp.k_norm_max = norms.data_ptr() if norms is not None else None
+    sp.B, sp.H, sp.S, sp.D = B, H, S, 128
+    with torch.cuda.device(dev):
+        st = lib.dtb_smooth_k(ctypes.byref(sp), _stream_ptr(dev))
+    _lib.check(st, "dtb_smooth_k")
+    return (out, norms) if want_norms else out
+
+
+smooth_k = _smooth_k   # public name; functions with a ``smooth_k`` flag call the underscored one
+
+
 def attention(
     query: torch.Tensor,
     key: torch.Tensor,
@@ -180,6 +224,7 @@ def attention(
     zero_padded_rows: bool = True,
     num_splits: int = 0,
     out: Optional[torch.Tensor] = None,
+    k_smoothed: bool = False,
 ) -> torch.Tensor:
     """Normalised joint attention, ``(B, heads, seq_q, dim)`` in ``query``'s dtype.
 
@@ -189,7 +234,10 @@ def attention(
     Keys at or past ``kv_len`` are masked; with ``zero_padded_rows`` query rows at or past it
     come back as exact zeros, so padding content cannot reach real rows or leak downstream.
     ``use_fixed_m`` selects the per-head constant-offset softmax for heads whose bound passes the
-    gate (``mk`` supplies a precomputed operand, otherwise it is derived from this call's q and k).
+    gate (``mk`` supplies a precomputed operand, otherwise it is derived from this call's q and k).  The wide
+    gate of 213 is safe only for k-smoothed keys (``diffusers_tpu/kernels/splash.py:596-598``): pass
+    ``k_smoothed=True`` when the caller has smoothed them (:func:`smooth_k`, as :func:`sdpa` does); otherwise
+    the operand is derived with the halved gate of 106.5, under which no row can flush whatever its mean logit.
     ``qk_fp8`` casts the pre-scaled query and the key to E4M3 and runs the score MMA in 8-bit floats.
     ``block_*``, ``kv_mask_all`` and ``unroll`` are accepted for signature parity and ignored.
     """
@@ -216,7 +264,8 @@ def attention(
         flags |= _lib.FLAG_ZERO_PADDED_ROWS
     if use_fixed_m:
         if mk is None:
-            mk = fixed_m_operands(query, key, scale=scale)
+            mk = fixed_m_operands(query, key, scale=scale,
+                                  gate=FIXED_M_SAFE_BOUND if k_smoothed else FIXED_M_RING_SAFE_BOUND)
         flags |= _lib.FLAG_BOUNDED_LOGITS
     else:
         mk = None
@@ -347,9 +396,14 @@ def sdpa(
     kv_len: KvLen = None,
     use_fixed_m: bool = False,
 ) -> torch.Tensor:
-    """SDPA-signature callable, ``[B, H, S, D]`` in and out (``mesh_attention.py:218-228``)."""
+    """SDPA-signature callable, ``[B, H, S, D]`` in and out (``mesh_attention.py:218-261``)."""
     del attn_mask, dropout_p, is_causal, enable_gqa  # Not supported, as in the reference.
-    return attention(query, key, value, scale=scale, kv_len=kv_len, use_fixed_m=use_fixed_m)
+    if use_fixed_m:
+        # The bounded-logit softmax and k-smoothing go together (mesh_attention.py:234-237): zero-mean keys make
+        # every row's largest logit non-negative, which the no-flush guarantee of the 213 gate rests on.
+        key = _smooth_k(key, kv_len=kv_len)
+        return attention(query, key, value, scale=scale, kv_len=kv_len, use_fixed_m=True, k_smoothed=True)
+    return attention(query, key, value, scale=scale, kv_len=kv_len)
 
 
 def qk_prepass(
@@ -364,7 +418,8 @@ def qk_prepass(
     kv_len: KvLen = None,
     scale: Optional[float] = None,
     want_mk: bool = False,
-    gate: float = FIXED_M_SAFE_BOUND,
+    gate: Optional[float] = None,
+    smooth_k: bool = False,
 ):
     """Fused per-head RMSNorm + rotary embedding + pad zeroing + ``(B, S, H, D) -> (B, H, S, D)``.
 
@@ -375,7 +430,12 @@ def qk_prepass(
     in f32 (``:191-195``); rows at or past ``kv_len[b]`` come out as zeros (``:372-381``).  Returns
     ``(q, k, v, mk)`` laid out ``(B, H, S, D)``; ``mk`` is the ``(2, H)`` bounded-logit operand of the returned
     q and k (``diffusers_tpu/kernels/fixed_m_bound.py:98-118``) when ``want_mk``, else ``None``.
+    ``smooth_k`` additionally subtracts the per-head mean key over the valid rows from the returned k
+    (``diffusers_tpu/models/minimax_h3/jax_server.py:276-281``); ``mk`` then bounds the smoothed keys.  ``gate``
+    defaults to 213 for smoothed keys and to 106.5 otherwise.
     """
+    if gate is None:
+        gate = FIXED_M_SAFE_BOUND if smooth_k else FIXED_M_RING_SAFE_BOUND
     tensors = [query, key] + ([value] if value is not None else [])
     for t in tensors:
         if not t.is_cuda:
@@ -424,6 +484,14 @@ def qk_prepass(
     with torch.cuda.device(dev):
         st = _lib.load().dtb_qk_prepass(ctypes.byref(p), _stream_ptr(dev))
     _lib.check(st, "dtb_qk_prepass")
+    if smooth_k:
+        # second pass over k only: the mean is a property of the finished (normed, rotated) keys
+        _, k_norms = _smooth_k(outs[1], kv_len=kv_len_t, out=outs[1], want_norms=True)
+        if want_mk:
+            with torch.cuda.device(dev):
+                st = _lib.load().dtb_fixed_m_from_norms(norms.data_ptr(), k_norms.data_ptr(), H, H, float(gate),
+                                                        mk.data_ptr(), _stream_ptr(dev))
+            _lib.check(st, "dtb_fixed_m_from_norms")
     return outs[0], outs[1], (outs[2] if value is not None else None), mk
 
 
@@ -493,6 +561,7 @@ def sparse_attention(
     mk: Optional[torch.Tensor] = None,
     zero_padded_rows: bool = True,
     out: Optional[torch.Tensor] = None,
+    k_smoothed: bool = False,
 ) -> torch.Tensor:
     """Block-sparse joint attention: each query block attends only to the key tiles its table row lists.
 
@@ -512,7 +581,8 @@ def sparse_attention(
     flags = _lib.FLAG_ZERO_PADDED_ROWS if (zero_padded_rows and kv_len_t is not None) else 0
     if use_fixed_m:
         if mk is None:
-            mk = fixed_m_operands(query, key, scale=scale)
+            mk = fixed_m_operands(query, key, scale=scale,
+                                  gate=FIXED_M_SAFE_BOUND if k_smoothed else FIXED_M_RING_SAFE_BOUND)
         flags |= _lib.FLAG_BOUNDED_LOGITS
     else:
         mk = None

@@ -30,6 +30,21 @@ def _(query, key, value, kv_len=None, scale=None):
     return torch.empty_like(query, memory_format=torch.contiguous_format)
 
 
+@torch.library.custom_op("dtb200::joint_attention_fixed_m", mutates_args=(), device_types="cuda")
+def joint_attention_fixed_m(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                            kv_len: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
+    """The bounded-logit variant together with the k-smoothing it presumes (``ours_splash_tt.py:126-137``)."""
+    return ops.sdpa(query, key, value, scale=scale, kv_len=kv_len, use_fixed_m=True)
+
+
+@joint_attention_fixed_m.register_fake
+def _(query, key, value, kv_len=None, scale=None):
+    return torch.empty_like(query, memory_format=torch.contiguous_format)
+
+
+FIXED_M = os.environ.get("DTB_FIXED_M", "0") == "1"   # the reference's torch backend runs use_fixed_m=True with smoothed keys
+
+
 _original_dispatch = None
 
 
@@ -46,7 +61,8 @@ def dispatch(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, 
                                   scale=scale, **kwargs)
     if not _already_bhsd:
         query, key, value = query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2)
-    out = torch.ops.dtb200.joint_attention(query, key, value, None, scale)
+    op = torch.ops.dtb200.joint_attention_fixed_m if FIXED_M else torch.ops.dtb200.joint_attention
+    out = op(query, key, value, None, scale)
     return out if _already_bhsd else out.transpose(1, 2)
 
 

@@ -191,6 +191,39 @@ int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* stream);
  * diffusers_tpu/backends/ours_splash_tt.py:189-213, and the operand pass diffusers_tpu/kernels/fixed_m_bound.py:57-118. */
 int dtb_qk_prepass(const dtb_prepass_params* pp, void* stream);
 
+/* Row chunks the key-smoothing pass sums separately (fixes the size of its scratch). */
+#define DTB_SMOOTH_K_CHUNKS 64
+
+/* k-smoothing of a bf16 [B, H, S, 128] key tensor: out = k - mean over the valid rows of k (f32 sum, mean rounded
+ * to bf16 before the subtraction), rows >= kv_len[b] written as zeros.  `out` may be `k` itself (in place).
+ * `scratch` holds dtb_smooth_k_scratch_bytes(B, H) bytes of device memory; `k_norm_max` (optional, [H] f32) receives
+ * the largest output row norm per head, the key half of the bounded-logit operand. */
+typedef struct dtb_smooth_k_params {
+  const void* k;
+  int64_t k_stride_b, k_stride_h, k_stride_s;
+  void* out;
+  int64_t out_stride_b, out_stride_h, out_stride_s;
+  const int32_t* kv_len; /* [B] or NULL */
+  void* scratch;
+  size_t scratch_bytes;
+  float* k_norm_max;     /* [H] or NULL */
+  int32_t B, H, S, D;
+} dtb_smooth_k_params;
+
+size_t dtb_smooth_k_scratch_bytes(int32_t B, int32_t H);
+
+/* The caller-side preconditioning the bounded-logit softmax presumes: zero-mean key columns make every query row's
+ * mean logit zero, hence its largest logit non-negative.  Replaces `k - mean(k, axis=2)` of
+ * diffusers_tpu/kernels/mesh_attention.py:234-237 and diffusers_tpu/backends/ours_splash_tt.py:136-137, and the
+ * padded form of diffusers_tpu/models/minimax_h3/jax_server.py:276-281. */
+int dtb_smooth_k(const dtb_smooth_k_params* sp, void* stream);
+
+/* mk[0,h] = ceil(q_norms[h] * k_norms[h / (Hq/Hkv)]), mk[1,h] = (that product <= gate), from per-head row-norm
+ * maxima already on the device (gate <= 0: 213).  Replaces diffusers_tpu/kernels/fixed_m_bound.py:98-118
+ * `fixed_m_operands` for norms collected by dtb_qk_prepass and dtb_smooth_k. */
+int dtb_fixed_m_from_norms(const float* q_norms, const float* k_norms, int32_t Hq, int32_t Hkv, float gate,
+                           float* mk_out, void* stream);
+
 /* Saturating E4M3 cast of a bf16 [B, H, S, 128] tensor, x * mult clamped to +-448, written contiguously; feeds the
  * DTB_FLAG_QK_FP8 variant of dtb_attn_fwd.  Replaces diffusers_tpu/kernels/fp8_cast.py:28-39 `quantize_saturating` as
  * applied to q and k in diffusers_tpu/kernels/splash.py:420-424. */

@@ -95,3 +95,44 @@ def test_python_api_refuses_cpu_tensors():
         dtb200.attention(q, q, q)
     with pytest.raises(ValueError, match="use_fixed_m needs"):
         dtb200.residual_attention(q, q, q, use_fixed_m=True)
+
+
+def test_broadcast_and_misaligned_views_are_rejected_before_any_launch():
+    """A stride of zero on an axis longer than one (an expanded K/V) cannot be described to TMA; scratch and
+    running-state pointers are accessed 16 bytes at a time.  Both are refused with a status, not a GPU fault."""
+    lib = _lib.load()
+    assert lib.dtb_attn_fwd(ctypes.byref(_params(k_stride_h=0)), None, 0, None) == 3      # DTB_ERR_SHAPE
+    assert lib.dtb_attn_fwd(ctypes.byref(_params(v_stride_s=0)), None, 0, None) == 3
+    assert lib.dtb_attn_fwd(ctypes.byref(_params(B=2, q_stride_b=0)), None, 0, None) == 3
+    # a size-1 axis may carry any stride
+    why = ctypes.c_int(-1)
+    lib.dtb_attn_supported(ctypes.byref(_params(Hq=1, Hkv=1, q_stride_h=0, k_stride_h=0, v_stride_h=0)), ctypes.byref(why))
+    assert why.value in (0, 5)                                                              # ok, or no sm_100 device here
+    # residual state / finalize: o_acc must be 16-byte aligned
+    r = _lib.AttnResidual(4104, 4096, 4096, 0, 0, 1)
+    assert lib.dtb_attn_fwd_residual(ctypes.byref(_params()), ctypes.byref(r), None) == 4   # DTB_ERR_ALIGN
+    assert lib.dtb_attn_finalize(ctypes.byref(_params()), ctypes.byref(r), None) == 4
+    # bounded-logit operand pass reads rows 8 bytes per lane
+    assert lib.dtb_fixed_m_operands(ctypes.byref(_params(q_stride_s=130)), ctypes.c_float(213.0), 4096, 4096, None) == 4
+
+
+def test_smooth_k_argument_validation():
+    lib = _lib.load()
+    assert lib.dtb_smooth_k_scratch_bytes(2, 3) == 64 * 2 * 3 * 128 * 4
+    sp = _lib.SmoothKParams()
+    assert lib.dtb_smooth_k(ctypes.byref(sp), None) == 1                                    # null pointers
+    sp.k = sp.out = sp.scratch = 4096
+    sp.B, sp.H, sp.S, sp.D = 1, 2, 256, 128
+    sp.k_stride_s = sp.out_stride_s = 128
+    sp.k_stride_h = sp.out_stride_h = 256 * 128
+    sp.k_stride_b = sp.out_stride_b = 2 * 256 * 128
+    sp.scratch_bytes = 16
+    assert lib.dtb_smooth_k(ctypes.byref(sp), None) == 6                                    # scratch too small
+    sp.scratch_bytes = lib.dtb_smooth_k_scratch_bytes(1, 2)
+    sp.k_stride_s = 132
+    assert lib.dtb_smooth_k(ctypes.byref(sp), None) == 4                                    # rows not 16-byte aligned
+    sp.k_stride_s = 128
+    sp.D = 64
+    assert lib.dtb_smooth_k(ctypes.byref(sp), None) == 3
+    assert lib.dtb_fixed_m_from_norms(None, None, 4, 4, ctypes.c_float(0.0), None, None) == 1
+    assert lib.dtb_fixed_m_from_norms(4096, 4096, 4, 3, ctypes.c_float(0.0), 4096, None) == 3
