@@ -198,11 +198,15 @@ cudaError_t ensure_kernel_attrs() {
   e = cudaFuncSetAttribute(attn_fwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(kSmemBytes));
   if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(attn_fwd_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kSmemBytes));
+  if (e != cudaSuccess) return e;
   // The register hand-over inside the kernel (setmaxnreg) is sized for kLaunchRegs registers per thread at
   // launch; with any other count a warpgroup could wait for registers that never come.  Refuse to launch then.
-  const void* variants[3] = {reinterpret_cast<const void*>(attn_fwd_kernel<false, false>),
+  const void* variants[4] = {reinterpret_cast<const void*>(attn_fwd_kernel<false, false>),
                              reinterpret_cast<const void*>(attn_fwd_kernel<true, false>),
-                             reinterpret_cast<const void*>(attn_fwd_kernel<false, true>)};
+                             reinterpret_cast<const void*>(attn_fwd_kernel<false, true>),
+                             reinterpret_cast<const void*>(attn_fwd_kernel<true, true>)};
   for (const void* fn : variants) {
     cudaFuncAttributes fa;
     e = cudaFuncGetAttributes(&fa, fn);
@@ -328,7 +332,6 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
 extern "C" int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_residual* r, void* stream) {
   int st = check_params(p, false);
   if (st != DTB_OK) return st;
-  if (p->flags & DTB_FLAG_QK_FP8) return DTB_ERR_UNSUPPORTED;
   if (r == nullptr || r->o_acc == nullptr || r->m == nullptr || r->l == nullptr) return DTB_ERR_NULL;
   if (reinterpret_cast<uintptr_t>(r->o_acc) & 15u) return DTB_ERR_ALIGN;
   if (!device_is_sm100()) return DTB_ERR_ARCH;
@@ -344,7 +347,10 @@ extern "C" int dtb_attn_fwd_residual(const dtb_attn_params* p, const dtb_attn_re
   kp.acc_init = r->init ? 1 : 0;
   kp.zero_padded_rows = 0;  // padded rows are zeroed by dtb_attn_finalize
   const dim3 grid(q_blocks(p), p->Hq, p->B);
-  attn_fwd_kernel<true, false><<<grid, dim3(kNumThreads), kSmemBytes, static_cast<cudaStream_t>(stream)>>>(kp);
+  if (p->flags & DTB_FLAG_QK_FP8)
+    attn_fwd_kernel<true, true><<<grid, dim3(kNumThreads), kSmemBytes, static_cast<cudaStream_t>(stream)>>>(kp);
+  else
+    attn_fwd_kernel<true, false><<<grid, dim3(kNumThreads), kSmemBytes, static_cast<cudaStream_t>(stream)>>>(kp);
   return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
 }
 

@@ -149,6 +149,25 @@ def fixed_m_operands(query: torch.Tensor, key: torch.Tensor, *, scale: Optional[
     return mk
 
 
+def row_norm_maxima(query: torch.Tensor, key: torch.Tensor, *, scale: Optional[float] = None
+                    ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(heads_q,)`` largest row norm of ``query * scale * log2(e)`` and ``(heads_kv,)`` largest key row norm, f32,
+    over batch and sequence (``fixed_m_query_norms`` / ``max_row_norm_per_head``,
+    ``diffusers_tpu/kernels/fixed_m_bound.py:57-95``): the two factors a sequence-parallel caller reduces with
+    MAX over its ranks before it forms the ring operand."""
+    _check_inputs(query, key, key)
+    query, key = _dense_last(query), _dense_last(key)
+    dev = query.device
+    norms = torch.empty(query.shape[1] + key.shape[1], dtype=torch.float32, device=dev)
+    mk = torch.empty(2, query.shape[1], dtype=torch.float32, device=dev)
+    p = _fill_params(query, key, key, None, None, None, scale, 0, 1, None)
+    with torch.cuda.device(dev):
+        st = _lib.load().dtb_fixed_m_operands(ctypes.byref(p), float(FIXED_M_SAFE_BOUND), norms.data_ptr(),
+                                              mk.data_ptr(), _stream_ptr(dev))
+    _lib.check(st, "dtb_fixed_m_operands")
+    return norms[:query.shape[1]], norms[query.shape[1]:]
+
+
 def quantize_e4m3(x: torch.Tensor, *, mult: float = 1.0) -> torch.Tensor:
     """Saturating E4M3 cast of a bf16 ``[B, H, S, 128]`` tensor: ``x * mult`` clamped to +-448, as
     ``diffusers_tpu/kernels/fp8_cast.py:28-39``.  Returns contiguous ``torch.float8_e4m3fn``."""
@@ -306,15 +325,37 @@ def residual_attention_(
     kv_len: KvLen = None,
     kv_offset: int = 0,
     q_offset: int = 0,
+    qk_fp8: bool = False,
 ) -> ResidualState:
-    """Folds one KV shard into ``state`` in place (the fused kernel + merge step of a ring)."""
-    _check_inputs(query, key, value)
+    """Folds one KV shard into ``state`` in place (the fused kernel + merge step of a ring).
+
+    With ``qk_fp8`` the score product runs on E4M3 operands (``diffusers_tpu/kernels/splash.py:420-424``):
+    ``query`` and ``key`` may be bf16 (cast here, the query pre-multiplied by ``scale * log2(e)``) or tensors
+    already cast with :func:`quantize_e4m3` the same way, which lets a ring cast its query once and move
+    one-byte key shards.
+    """
     if use_fixed_m and mk is None:
         raise ValueError("use_fixed_m needs the (2, heads) operand mk.")
-    query, key, value = _dense_last(query), _dense_last(key), _dense_last(value)
+    if qk_fp8:
+        s_ = (1.0 / math.sqrt(query.shape[-1])) if scale is None else float(scale)
+        if query.dtype == torch.bfloat16:
+            query = quantize_e4m3(query, mult=s_ * LOG2_E)
+        if key.dtype == torch.bfloat16:
+            key = quantize_e4m3(key)
+        if query.dtype != torch.float8_e4m3fn or key.dtype != torch.float8_e4m3fn:
+            raise NotImplementedError("qk_fp8 takes bf16 or float8_e4m3fn query and key")
+        _check_inputs(value, value, value)
+        if query.dim() != 4 or key.shape != value.shape or query.shape[0] != key.shape[0] or query.shape[-1] != 128:
+            raise ValueError("query/key/value shapes do not match")
+        query, key = query.contiguous(), key.contiguous()
+        scale = 1.0 / LOG2_E          # the logits already are in log2 units
+    else:
+        _check_inputs(query, key, value)
+        query, key = _dense_last(query), _dense_last(key)
+    value = _dense_last(value)
     dev = query.device
     kv_len_t = _kv_len_tensor(kv_len, query.shape[0], dev)
-    flags = _lib.FLAG_BOUNDED_LOGITS if use_fixed_m else 0
+    flags = (_lib.FLAG_BOUNDED_LOGITS if use_fixed_m else 0) | (_lib.FLAG_QK_FP8 if qk_fp8 else 0)
     p = _fill_params(query, key, value, None, kv_len_t, mk if use_fixed_m else None, scale, flags, 1,
                      _status_buffer(dev))
     r = _lib.AttnResidual(state.o.data_ptr(), state.m.data_ptr(), state.l.data_ptr(), int(kv_offset),
@@ -372,14 +413,12 @@ def residual_attention(
     ``use_fixed_m`` is set without ``mk``, as the reference does at ``:712-713``).
     """
     del block_q, block_kv, block_kv_compute
-    if qk_fp8:
-        raise NotImplementedError("qk_fp8 (E4M3 Q/K) is not built yet")
     if use_fixed_m and mk is None:
         raise ValueError("use_fixed_m needs the (2, heads) operand mk.")
     _check_inputs(query, key, value)
     state = ResidualState(query.shape[0], query.shape[1], query.shape[2], query.device)
     residual_attention_(state, query, key, value, scale=scale, use_fixed_m=use_fixed_m, mk=mk, kv_len=kv_len,
-                        kv_offset=kv_offset)
+                        kv_offset=kv_offset, qk_fp8=qk_fp8)
     return state.o, state.m.unsqueeze(-1), state.l.unsqueeze(-1)
 
 

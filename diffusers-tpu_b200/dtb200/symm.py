@@ -61,6 +61,8 @@ class SymmArena:
 
     def peer(self, rank: int, offset: int, shape, dtype=torch.bfloat16) -> torch.Tensor:
         esz = torch.empty((), dtype=dtype).element_size()
+        if esz == 1:     # one-byte types are mapped as bytes and reinterpreted
+            return self.handle.get_buffer(rank, tuple(shape), torch.uint8, offset).view(dtype)
         return self.handle.get_buffer(rank, tuple(shape), dtype, offset // esz)
 
     def ptr(self, rank: int, offset: int) -> int:
@@ -129,19 +131,31 @@ class UlyssesP2P:
 
 
 class RingPull:
-    """Ring-KV attention where each step's K/V shard is pulled from its owner by the copy engines."""
+    """Ring-KV attention where each step's K/V shard is pulled from its owner by the copy engines.
 
-    def __init__(self, batch: int, heads: int, seq_local: int, group=None, device: Optional[torch.device] = None):
+    ``qk_fp8`` moves and multiplies E4M3 keys (half the bytes per K shard) and casts the pre-scaled query once
+    per call; with ``use_fixed_m`` every step runs the bounded-logit softmax with one operand for the whole ring
+    (``diffusers_tpu/kernels/fixed_m_bound.py:121-155``: the same ``m`` for all heads, the gate halved because
+    ring shards are not k-smoothed) — the reference's fastest ring configuration (``:313-316``).
+    """
+
+    def __init__(self, batch: int, heads: int, seq_local: int, group=None, device: Optional[torch.device] = None,
+                 qk_fp8: bool = False):
         self.P = dist.get_world_size(group)
+        self.group = group
         self.B, self.H, self.Sl = batch, heads, seq_local
-        shard = batch * heads * seq_local * D * 2
-        self.arena = SymmArena(2 * shard + 4096, group, device)
+        self.qk_fp8 = qk_fp8
+        self.k_dtype = torch.float8_e4m3fn if qk_fp8 else torch.bfloat16
+        v_shard = batch * heads * seq_local * D * 2
+        k_shard = v_shard // 2 if qk_fp8 else v_shard
+        self.arena = SymmArena(k_shard + v_shard + 4096, group, device)
         self.rank = self.arena.rank
-        self.k_off, self.v_off = self.arena.carve(shard), self.arena.carve(shard)
+        self.k_off, self.v_off = self.arena.carve(k_shard), self.arena.carve(v_shard)
         shape = (batch, heads, seq_local, D)
         dev = self.arena.device
-        self.k_pub, self.v_pub = self.arena.local(self.k_off, shape), self.arena.local(self.v_off, shape)
-        self.bufs = [(torch.empty(shape, dtype=torch.bfloat16, device=dev),
+        self.k_pub = self.arena.local(self.k_off, shape, self.k_dtype)
+        self.v_pub = self.arena.local(self.v_off, shape)
+        self.bufs = [(torch.empty(shape, dtype=self.k_dtype, device=dev),
                       torch.empty(shape, dtype=torch.bfloat16, device=dev)) for _ in range(2)] if self.P > 1 else []
         self.copy_stream = torch.cuda.Stream(dev)
         self.ready = [torch.cuda.Event() for _ in range(2)]
@@ -152,12 +166,39 @@ class RingPull:
     def schedule(self) -> List[int]:
         return [(self.rank - t) % self.P for t in range(self.P)]
 
+    def ring_operand(self, q: torch.Tensor, k: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+        """The ``(2, heads)`` bounded-logit operand of a whole ring: per-head row-norm maxima of this rank's shards,
+        reduced with MAX over the ranks, then ``fixed_m.ring_fixed_m_operands``.  Callers with calibrated norms
+        (``fixed_m.static_fixed_m_operands``) pass their own ``mk`` instead and skip this pass."""
+        from . import fixed_m
+
+        qn, kn = ops.row_norm_maxima(q, k, scale=scale)
+        if self.P > 1:
+            both = torch.cat([qn, kn])
+            dist.all_reduce(both, op=dist.ReduceOp.MAX, group=self.group)
+            qn, kn = both[:qn.numel()], both[qn.numel():]
+        if kn.numel() != qn.numel():
+            kn = kn.repeat_interleave(qn.numel() // kn.numel())
+        if self.qk_fp8:
+            qn = qn * (1.0 + 2.0 ** -4)      # E4M3 rounding can raise a magnitude by 2^-4, on q and on k (:293-297)
+            kn = kn * (1.0 + 2.0 ** -4)
+        return fixed_m.ring_fixed_m_operands(qn, kn)
+
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, kv_len=None, scale: Optional[float] = None,
-                 out: Optional[torch.Tensor] = None, zero_padded_rows: bool = True) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, zero_padded_rows: bool = True, use_fixed_m: bool = False,
+                 mk: Optional[torch.Tensor] = None) -> torch.Tensor:
         dev = self.arena.device
         main = torch.cuda.current_stream(dev)
         Sl = self.Sl
         sched = self.schedule()
+        if use_fixed_m and mk is None:
+            mk = self.ring_operand(q, k, scale)
+        if self.qk_fp8:
+            import math
+
+            s_ = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+            q = ops.quantize_e4m3(q, mult=s_ * ops.LOG2_E)
+            k = ops.quantize_e4m3(k)
         if self.P > 1:
             self.k_pub.copy_(k)
             self.v_pub.copy_(v)
@@ -174,11 +215,11 @@ class RingPull:
                     if t == 0:
                         self.copy_stream.wait_stream(main)       # after the barrier
                     self.copy_stream.wait_event(self.consumed[t % 2])
-                    kb.copy_(self.arena.peer(nxt, self.k_off, self.shape), non_blocking=True)
+                    kb.copy_(self.arena.peer(nxt, self.k_off, self.shape, self.k_dtype), non_blocking=True)
                     vb.copy_(self.arena.peer(nxt, self.v_off, self.shape), non_blocking=True)
                     self.ready[t % 2].record(self.copy_stream)
             ops.residual_attention_(self.state, q, k_cur, v_cur, scale=scale, kv_len=kv_len, kv_offset=origin * Sl,
-                                    q_offset=self.rank * Sl)
+                                    q_offset=self.rank * Sl, use_fixed_m=use_fixed_m, mk=mk, qk_fp8=self.qk_fp8)
             if t >= 1:
                 self.consumed[(t - 1) % 2].record(main)          # the buffer step t read may be refilled
             if t + 1 < self.P:

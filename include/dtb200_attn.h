@@ -39,7 +39,7 @@ enum dtb_status {
 /* Flags for dtb_attn_params.flags */
 #define DTB_FLAG_ZERO_PADDED_ROWS 0x1u /* write exact zeros to query rows >= kv_len[b]            */
 #define DTB_FLAG_BOUNDED_LOGITS 0x2u   /* per-head constant softmax offset from `mk` (fixed-m)    */
-#define DTB_FLAG_QK_FP8 0x8u           /* q and k are E4M3 bytes (strides in bytes); dtb_attn_fwd only */
+#define DTB_FLAG_QK_FP8 0x8u           /* q and k are E4M3 bytes (strides in bytes); dtb_attn_fwd and dtb_attn_fwd_residual */
 
 /* One attention call.  All pointers are device pointers unless noted. */
 typedef struct dtb_attn_params {
@@ -180,8 +180,10 @@ int dtb_fixed_m_operands(const dtb_attn_params* p, float gate, float* norms, flo
  * stays resident on every device that loads it.  The call allocates nothing.  Calls whose partials
  * would not fit return DTB_ERR_WORKSPACE (dtb_last_error_detail() gives both sizes); p->num_splits
  * is honoured as in dtb_attn_fwd.  The first call on each device looks up the array's device address;
- * make that first call outside any stream capture.  All calls on a device share the array: calls that
- * may overlap on the GPU race and must be ordered by the caller.
+ * make that first call outside any stream capture.  The address is kept per device ordinal for the life of
+ * the process and is not looked up again after a cudaDeviceReset: do not reset a device this entry point has
+ * been used on.  All calls on a device share the array: calls that may overlap on the GPU race and must be
+ * ordered by the caller.
  * This entry point has no counterpart in the reference project. */
 int dtb_attn_fwd_static_scratch(const dtb_attn_params* p, void* stream);
 

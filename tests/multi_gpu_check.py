@@ -1,6 +1,12 @@
 """Run under torchrun on N GPUs: checks a multi-GPU driver against the CPU oracle on sampled rows.
 
-    python -m torch.distributed.run --nproc-per-node N tests/multi_gpu_check.py {ulysses|ring|ulysses-p2p|ring-pull} [S] [H] [B]
+    python -m torch.distributed.run --nproc-per-node N tests/multi_gpu_check.py MODE [S] [H] [B]
+
+MODE: ulysses | ring (NCCL collectives), ulysses-p2p | ring-pull (this library's peer-memory kernels),
+ring-pull-fixed-m (bounded-logit softmax with the ring operand), ring-pull-fp8 (E4M3 q/k + that operand).
+Inputs are generated shard by shard on the GPUs (no rank ever builds the whole tensor on the host); for the
+check every rank gathers the keys and values of two heads and compares a strided sample of its own query rows,
+plus its last rows, with the fp32 oracle.
 """
 import os
 import sys
@@ -16,6 +22,20 @@ import dtb200  # noqa: E402
 from dtb200 import parallel  # noqa: E402
 from oracle import attn_oracle as O  # noqa: E402
 
+CHECK_HEADS = 2
+SAMPLE_ROWS = 96
+TAIL_ROWS = 32
+
+
+def make_shard(B, H, Sl, rank, dev):
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q = torch.randn(B, H, Sl, 128, generator=g, device=dev)
+    k = torch.randn(B, H, Sl, 128, generator=g, device=dev)
+    v = torch.randn(B, H, Sl, 128, generator=g, device=dev)
+    q = (q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True)) * 2).to(torch.bfloat16)
+    k = (k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True))).to(torch.bfloat16)
+    return q, k, v.to(torch.bfloat16)
+
 
 def main():
     mode = sys.argv[1]
@@ -26,32 +46,50 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    g = torch.Generator().manual_seed(123)
-    q, k, v = (torch.randn(B, H, S, 128, generator=g) for _ in range(3))
-    q = (q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True)) * 2).to(torch.bfloat16)
-    k = (k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True))).to(torch.bfloat16)
-    v = v.to(torch.bfloat16)
-    kv_len = torch.tensor([S - 17 * (b + 1) for b in range(B)], dtype=torch.int32)
+    assert S % world == 0, "the sequence must divide over the ranks"
     Sl = S // world
-    sl = slice(rank * Sl, (rank + 1) * Sl)
-    shard = [t[:, :, sl].contiguous().to(dev) for t in (q, k, v)]
+    q, k, v = make_shard(B, H, Sl, rank, dev)
+    kv_len = torch.tensor([S - 17 * (b + 1) for b in range(B)], dtype=torch.int32)
+    fp8 = mode == "ring-pull-fp8"
     if mode in ("ulysses", "ring"):
         fn = parallel.ulysses_attention if mode == "ulysses" else parallel.ring_attention
-        out = fn(*shard, kv_len=kv_len.to(dev))
+        out = fn(q, k, v, kv_len=kv_len.to(dev))
     else:
         from dtb200 import symm
 
-        cls = symm.UlyssesP2P if mode == "ulysses-p2p" else symm.RingPull
-        op = cls(B, H, Sl, device=dev)
+        if mode == "ulysses-p2p":
+            op, kw = symm.UlyssesP2P(B, H, Sl, device=dev), {}
+        else:
+            op = symm.RingPull(B, H, Sl, device=dev, qk_fp8=fp8)
+            kw = {"use_fixed_m": mode != "ring-pull"}
         for _ in range(2):      # twice: buffers are reused across calls
-            out = op(*shard, kv_len=kv_len.to(dev)).clone()
+            out = op(q, k, v, kv_len=kv_len.to(dev), **kw).clone()
     dtb200.check_device_status(dev)
-    rows = torch.arange(rank * Sl, (rank + 1) * Sl, max(1, Sl // 64))
-    ref = O.attention_fp32(q, k, v, kv_len=kv_len, rows=rows)
-    err = (out[:, :, (rows - rank * Sl).to(dev)].float().cpu() - ref).abs()
+
+    # oracle on the first CHECK_HEADS heads: whole keys and values gathered, a sample of this rank's query rows
+    hs = min(CHECK_HEADS, H)
+    parts_k = [torch.empty(B, hs, Sl, 128, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    parts_v = [torch.empty_like(parts_k[0]) for _ in range(world)]
+    dist.all_gather(parts_k, k[:, :hs].contiguous())
+    dist.all_gather(parts_v, v[:, :hs].contiguous())
+    k_all, v_all = torch.cat(parts_k, dim=2), torch.cat(parts_v, dim=2)
+    local_rows = torch.cat([torch.arange(0, Sl, max(1, Sl // SAMPLE_ROWS)), torch.arange(max(Sl - TAIL_ROWS, 0), Sl)]).unique()
+    q_s = q[:, :hs, local_rows.to(dev)]
+    scale = None
+    if fp8:   # the variant is compared on the operands it multiplies (E4M3 q * scale * log2e and k)
+        c = (128 ** -0.5) * O.LOG2_E
+        q_s = dtb200.quantize_e4m3(q_s.contiguous(), mult=c).float()
+        k_all = dtb200.quantize_e4m3(k_all).float()
+        scale = 1.0 / O.LOG2_E
+    ref = O.attention_fp32(q_s, k_all, v_all, kv_len=kv_len, scale=scale, zero_padded_rows=False)
+    global_rows = local_rows + rank * Sl
+    for b in range(B):
+        ref[b, :, global_rows >= int(kv_len[b])] = 0
+    err = (out[:, :hs, local_rows.to(dev)].float().cpu() - ref).abs()
     ok = torch.tensor([float(err.max() <= 2e-2 and err.mean() <= 2e-3)], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    print(f"rank {rank}: max_abs={err.max().item():.3e} mean_abs={err.mean().item():.3e}", flush=True)
+    print(f"rank {rank}: {mode} S={S} H={H} B={B} rows={len(local_rows)} max_abs={err.max().item():.3e} "
+          f"mean_abs={err.mean().item():.3e}", flush=True)
     if rank == 0:
         print("PARITY OK" if ok.item() == 1.0 else "PARITY FAILED", flush=True)
     dist.destroy_process_group()

@@ -255,6 +255,40 @@ def test_qk_fp8_variant_matches_oracle_on_quantised_operands(B, H, S, kv_len):
     assert err.max().item() <= 0.25 and err.mean().item() <= 2e-2
 
 
+def test_residual_ring_with_e4m3_scores_and_the_ring_operand():
+    """The reference's fastest ring configuration: E4M3 q/k with the bounded-logit softmax on one operand for all
+    steps (``fixed_m_bound.py:121-155, 313-316``).  Four shards folded in ring order, against the oracle on the same
+    quantised operands."""
+    from dtb200 import fixed_m as F
+
+    B, H, S, n = 2, 3, 1024, [1000, 1024]
+    q, k, v = _rand(B, H, S, S, seed=41, gain=1.5)
+    c = (128 ** -0.5) * F.LOG2_E
+    q8, k8 = dtb200.quantize_e4m3(q.to(DEV), mult=c), dtb200.quantize_e4m3(k.to(DEV))
+    qn, kn = dtb200.ops.row_norm_maxima(q.to(DEV), k.to(DEV))
+    assert torch.allclose(qn.cpu(), F.fixed_m_query_norms(q), rtol=1e-5) and torch.allclose(kn.cpu(), F.max_row_norm_per_head(k), rtol=1e-5)
+    mk = F.ring_fixed_m_operands(qn * (1 + 2.0 ** -4), kn * (1 + 2.0 ** -4))
+    assert torch.all(mk[1] == 1.0) and torch.all(mk[0] == 106.0)
+    ref = O.attention_fp32(q8.float().cpu(), k8.float().cpu(), v, kv_len=n, scale=1.0 / F.LOG2_E)
+    for pre_cast in (False, True):
+        state = dtb200.ResidualState(B, H, S, torch.device(DEV))
+        for i in (1, 0, 3, 2):
+            sl = slice(i * 256, (i + 1) * 256)
+            ks = (k8 if pre_cast else k.to(DEV))[:, :, sl].contiguous()
+            dtb200.residual_attention_(state, q8 if pre_cast else q.to(DEV), ks, v[:, :, sl].contiguous().to(DEV),
+                                       kv_len=n, kv_offset=i * 256, use_fixed_m=True, mk=mk, qk_fp8=True)
+        assert torch.all(state.m == 106.0 - 88.0)
+        _check(dtb200.finalize_residual(state, kv_len=n), ref, n)
+    o, m, l = dtb200.residual_attention(q.to(DEV), k.to(DEV), v.to(DEV), qk_fp8=True)   # online softmax, one shard
+    _check(dtb200.finalize_residual(_state_of(o, m, l)), O.attention_fp32(q8.float().cpu(), k8.float().cpu(), v, scale=1.0 / F.LOG2_E))
+
+
+def _state_of(o, m, l):
+    st = dtb200.ResidualState(o.shape[0], o.shape[1], o.shape[2], o.device)
+    st.o, st.m, st.l, st.fresh = o, m.squeeze(-1).contiguous(), l.squeeze(-1).contiguous(), False
+    return st
+
+
 def test_full_size_properties_config2():
     """At full size: linearity in V and invariance to k-smoothing, which need no oracle pass."""
     cfg = CONFIGS["c2_image1024"]

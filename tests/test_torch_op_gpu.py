@@ -45,16 +45,39 @@ def test_dispatch_hook_layout_and_fallback_rules():
         torch_op.dispatch(*bshd, is_causal=True)
 
 
-@pytest.mark.parametrize("mode", ["ulysses", "ring", "ulysses-p2p", "ring-pull"])
-def test_two_gpu_drivers(mode):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29631", os.path.join(ROOT, "tests", "multi_gpu_check.py"), mode]
+def _run_ranks(n, mode, *shape):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", os.path.join(ROOT, "tests", "multi_gpu_check.py"), mode, *map(str, shape)]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "PARITY OK" in r.stdout
+
+
+@pytest.mark.parametrize("mode,shape", [
+    ("ulysses", ()), ("ring", ()), ("ulysses-p2p", ()), ("ring-pull", ()),
+    ("ring-pull-fixed-m", ()), ("ring-pull-fp8", ()),
+    ("ring-pull", (87824, 5, 1)),            # two of the eight 43,912-row shards of the 351,296-token video shape
+    ("ulysses-p2p", (16896, 24, 2)),         # the 2048 x 2048 image shape, 12 heads per rank
+])
+def test_two_gpu_drivers(mode, shape):
+    """Needs two GPUs; on a one-GPU machine these are skipped and the multi-GPU drivers are covered only by the
+    gloo tests of their host logic and by the one-GPU emulation of the peer-store kernels below."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run_ranks(2, mode, *shape)
+
+
+@pytest.mark.parametrize("mode,shape", [
+    ("ring-pull", (351296, 5, 1)),           # the ring of the 351,296-token video shape, 5 of its 40 heads
+    ("ring-pull-fp8", (351296, 5, 1)),
+    ("ulysses-p2p", (48872, 40, 2)),         # the 480p video shape: 40 heads -> 5 per rank, ragged 6,109-row shards
+    ("ulysses", (16896, 24, 2)),
+])
+def test_eight_gpu_drivers(mode, shape):
+    if torch.cuda.device_count() < 8:
+        pytest.skip("needs 8 GPUs")
+    _run_ranks(8, mode, *shape)
 
 
 def test_scatter_entry_points_with_local_buffers_as_peers():

@@ -17,6 +17,7 @@ import torch
 
 import dtb200
 from dtb200 import _lib, ops
+from oracle import attn_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -62,6 +63,9 @@ def test_static_scratch_matches_workspace_path_twice_in_a_row():
         err = (got.float() - want.float()).abs()
         assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3
         assert torch.equal(got, want)
+        # and both are right: the fp32 oracle on the same inputs
+        err = (got.float().cpu() - O.attention_fp32(q, k, v, kv_len=kv_len)).abs()
+        assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3
         free_now = torch.cuda.mem_get_info()[0]
         if free_after_first is None:
             free_after_first = free_now
@@ -90,3 +94,21 @@ def test_static_scratch_unsplit_call_needs_no_scratch():
     want = dtb200.attention(q, k, v, kv_len=1000, num_splits=1)
     dtb200.check_device_status(DEV)
     assert torch.equal(got, want)
+
+
+def test_static_scratch_with_automatic_split_selection():
+    """num_splits = 0: the library picks the split itself (a short-query call that leaves most SMs idle
+    unsplit) and sizes its use of the built-in array accordingly.  Twice in a row, against the ordinary entry
+    point and the fp32 oracle."""
+    q, k, v = _inputs(1, 2, 256, 8192, seed=52)
+    p = ops._fill_params(q, k, v, torch.empty_like(q), None, None, None, 0, 0, None)
+    assert _lib.load().dtb_attn_workspace_bytes(ctypes.byref(p)) > 0          # the automatic choice does split this call
+    want = dtb200.attention(q, k, v, kv_len=[8000], num_splits=0)
+    ref = O.attention_fp32(q, k, v, kv_len=[8000])
+    for _ in range(2):
+        st, got = _static_scratch_call(q, k, v, [8000], 0)
+        _lib.check(st, "dtb_attn_fwd_static_scratch")
+        dtb200.check_device_status(DEV)
+        for other in (want.float().cpu(), ref):
+            err = (got.float().cpu() - other).abs()
+            assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3
