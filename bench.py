@@ -16,6 +16,13 @@ on chip halves: batch elements first, then heads, are dealt to ranks and every r
 kernel on its resident shard (no collective on the data path).  ``--mode ulysses`` starts and ends
 sequence-sharded with an all-to-all either side; ``--mode ring`` rotates K/V shards between ranks.
 
+Besides the headline line every run also measures, in the same process and on the same GPUs, the collective
+placements on the long shapes (``workloads`` in the JSON line): the 48,872-token video shape head-parallel with
+the exchange either side of the kernel (Ulysses), the 351,296-token shape as a ring over K/V shards, and the
+2048 x 2048 image shape with CFG halves on chip halves - each with this library's peer-memory kernels and, beside
+it, over NCCL collectives, and each with the one-GPU time of the same call measured in the same run (every rank
+runs the whole call as a replica) so that the scaling efficiency needs no number from another run.
+
 ``--impl reference`` times the CPU restatement of the reference's own CPU attention (fp32 softmax)
 on the host cores for the same workload and metric, on a bounded sample per step.
 """
@@ -40,9 +47,27 @@ import torch  # noqa: E402
 METRIC = "attention_tflops"
 UNIT = "TFLOP/s"
 LAYERS = {"c1_image512_cpu": 60, "c2_image1024": 60, "c3_image2048": 20, "c4_video480p": 4, "c5_video768p": 1}
-# DRAM bytes per launch of attn_fwd_kernel on the c2 workload (dram__bytes_read.sum + dram__bytes_write.sum),
-# from the ncu capture summarised in profiles/attn_fwd_kernel_c2_image1024.md (algorithmic bytes: 226 MB).
-NCU_TRAFFIC_BYTES_C2 = 199_908_864
+PROFILE_SUMMARY = os.path.join(ROOT, "profiles", "attn_fwd_kernel_c2_image1024.md")
+
+
+def profiled_traffic_bytes():
+    """DRAM bytes per launch of the attention kernel on the c2 workload as the committed ncu summary records them
+    (``dram__bytes_read.sum`` + ``dram__bytes_write.sum`` of its last captured launch), or None."""
+    try:
+        text = open(PROFILE_SUMMARY).read()
+    except OSError:
+        return None
+    total = 0.0
+    for key in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+        row = next((ln for ln in text.splitlines() if ln.startswith("| " + key)), None)
+        if row is None:
+            return None
+        cell = [c.strip() for c in row.strip("|").split("|")][-1]
+        try:
+            total += float(cell.split()[0]) * {"MB": 1e6, "GB": 1e9, "KB": 1e3}[cell.split()[1]]
+        except (ValueError, KeyError, IndexError):
+            return None
+    return total
 
 
 def measured_peaks():
@@ -293,15 +318,179 @@ def run_ours(args, cfg):
         e2e_ms, e2e_steps, h2d_bytes, d2h_bytes = run_e2e(args, mode, layers, sets, world, dev, group, barrier, fused)
     dtb200.check_device_status(dev)
 
+    h2d_rates = None
+    if e2e_ms is not None:
+        # host->device rate this rank saw (its share of the step's input bytes over its own elapsed time)
+        mine = torch.tensor([h2d_bytes / world * e2e_steps / (e2e_ms * 1e-3) / 1e9], device=dev, dtype=torch.float64)
+        if world > 1:
+            allr = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(allr, mine)
+            h2d_rates = [round(x.item(), 1) for x in allr]
+        else:
+            h2d_rates = [round(mine.item(), 1)]
     if world > 1:
         t = torch.tensor([ms_total, e2e_ms or 0.0], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = t[0].item()
         e2e_ms = t[1].item() if e2e_ms is not None else None
-    finish(args, cfg, mode, layers, sets, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
-           h2d_bytes, d2h_bytes, launches_per_call, clocks)
+    del fused
+    sets_info = (len(sets), 3 * sets[0][0].numel() * 2 / 1e6)
+    sets.clear()
+    torch.cuda.empty_cache()
+    workloads = None
+    if not args.no_workloads and args.workload == "c2_image1024" and mode == "local":
+        workloads = run_workloads(args, world, rank, local, dev)
+    finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
+           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates)
     if world > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------------
+# collective placements on the long shapes, with the one-GPU time of the same call measured beside them
+# --------------------------------------------------------------------------------------------
+WORKLOAD_CALLS = {"c3_image2048": (3, 12), "c4_video480p": (3, 4), "c5_video768p": (3, 2)}   # (warm-up, timed)
+
+
+def _timed_calls(fn, sets, warmup, calls, world, rank, local, dev):
+    """ms per call (max over ranks, CUDA events on the launching stream) and the SM clock sampled meanwhile."""
+    import torch.distributed as dist
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(warmup):
+        fn(sets[i % len(sets)])
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(calls):
+        fn(sets[i % len(sets)])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / calls
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    return ms, clocks
+
+
+def _n_sets(bytes_per_set):
+    """Rotating input sets so that consecutive calls do not find their inputs in the 126 MB L2."""
+    return int(max(1, min(6, -(-300e6 // max(bytes_per_set, 1)))))
+
+
+def run_workloads(args, world, rank, local, dev):
+    """The collective placements, each as ``{ms_per_call, tflops, frac_of_burst_per_gpu, n1_ms_per_call,
+    efficiency_vs_n1, sm_mhz, ...}``; at one GPU only the local kernel on the whole call."""
+    import torch.distributed as dist
+
+    import dtb200
+    from dtb200 import parallel
+    from dtb200.inputs import CONFIGS, make_inputs
+
+    burst, _, _ = measured_peaks()
+    plan = [("c4_video480p", "ulysses", False), ("c5_video768p", "ring", False), ("c3_image2048", "ulysses", True)]
+    if world == 8:
+        plan.append(("c5_video768p", "ulysses", False))
+    results = {}
+    n1_cache = {}
+    subgroups = {}
+
+    def record(key, cfg, ms, clocks, extra):
+        tf = cfg.flops() / (ms * 1e-3) / 1e12
+        entry = {"ms_per_call": ms, "tflops": tf, "frac_of_burst_per_gpu": tf / (burst * world),
+                 "sm_mhz": clocks["sm_mhz"] if clocks else None,
+                 "clock_reasons": clocks["reasons"] if clocks else None}
+        entry.update(extra)
+        results[key] = entry
+        return entry
+
+    for name, mode, cfg_halves in plan:
+        cfg = CONFIGS[name]
+        warmup, calls = WORKLOAD_CALLS[name]
+        # ---- one GPU: every rank runs the whole call on its own GPU (replicas), max over ranks
+        if name not in n1_cache:
+            q, k, v, kv_len = make_inputs(cfg, 0, device="cuda")
+            o = torch.empty_like(q)
+            ms1, clk1 = _timed_calls(lambda s: dtb200.attention(s[0], s[1], s[2], kv_len=s[3], out=s[4]),
+                                     [(q, k, v, kv_len, o)], warmup, calls, world, rank, local, dev)
+            dtb200.check_device_status(dev)
+            n1_cache[name] = ms1
+            record(f"{name}/1gpu", cfg, ms1, clk1,
+                   {"n_gpus_used": 1, "parallelism": "local kernel on the whole call" +
+                    (f" ({world} replicas, slowest)" if world > 1 else ""),
+                    "frac_of_burst_per_gpu": cfg.flops() / (ms1 * 1e-3) / 1e12 / burst,
+                    "l2": "one input set; q/k/v of a call are larger than L2"})
+            del q, k, v, o
+            torch.cuda.empty_cache()
+        if world == 1:
+            continue
+        ms1 = n1_cache[name]
+        # ---- N GPUs, sequence-sharded in and out
+        group, groups, sub_world, sub_rank, my_cfg = None, 1, world, rank, 0
+        if cfg_halves and cfg.batch > 1 and world % cfg.batch == 0 and world > cfg.batch:
+            groups = cfg.batch
+            if groups not in subgroups:
+                for ranks in parallel.cfg_subgroups(world, groups):
+                    g = dist.new_group(ranks)
+                    if rank in ranks:
+                        subgroups[groups] = g
+            group = subgroups[groups]
+            sub_world = world // groups
+            sub_rank, my_cfg = rank % sub_world, rank // sub_world
+        if cfg.heads % sub_world and mode == "ulysses":
+            continue
+        shard_bytes = 3 * (cfg.batch // groups) * cfg.heads * (cfg.seq // sub_world) * 256
+        sets = []
+        for i in range(_n_sets(shard_bytes)):
+            q, k, v, kv_len = parallel.make_sequence_shard(cfg, i, sub_rank, sub_world, dev)
+            if groups > 1:
+                q, k, v = (t[my_cfg:my_cfg + 1].contiguous() for t in (q, k, v))
+                kv_len = kv_len[my_cfg:my_cfg + 1].contiguous()
+            sets.append((q, k, v, kv_len, torch.empty_like(q)))
+        shp = sets[0][0].shape
+        placement = (f"cfg{groups} x " if groups > 1 else "") + f"{mode}{sub_world}"
+        for transport in ("p2p", "nccl"):
+            if transport == "p2p":
+                from dtb200 import symm
+
+                cls = symm.UlyssesP2P if mode == "ulysses" else symm.RingPull
+                op = cls(shp[0], shp[1], shp[2], group=group, device=dev)
+                if mode == "ulysses":
+                    fn = lambda s: op(s[0], s[1], s[2], kv_len=s[3])
+                else:
+                    fn = lambda s: op(s[0], s[1], s[2], kv_len=s[3], out=s[4])
+                how = ("peer-store exchange fused into the scatter and attention kernels" if mode == "ulysses"
+                       else "copy-engine pulls of K/V shards under the residual kernel")
+            else:
+                op = None
+                if mode == "ulysses":
+                    fn = lambda s: parallel.ulysses_attention(s[0], s[1], s[2], kv_len=s[3], out=s[4], group=group)
+                    how = "NCCL all-to-all either side of the kernel"
+                else:
+                    fn = lambda s: parallel.ring_attention(s[0], s[1], s[2], kv_len=s[3], out=s[4], group=group)
+                    how = "NCCL send/recv rotation of K/V shards"
+            ms, clk = _timed_calls(fn, sets, warmup, calls, world, rank, local, dev)
+            dtb200.check_device_status(dev)
+            record(f"{name}/{placement}/{transport}", cfg, ms, clk,
+                   {"n_gpus_used": world, "parallelism": f"{placement}: {how}", "n1_ms_per_call": ms1,
+                    "efficiency_vs_n1": ms1 / (world * ms),
+                    "l2": f"{len(sets)} rotating input sets of {shard_bytes / 1e6:.0f} MB per rank"})
+            del op, fn
+            torch.cuda.empty_cache()
+        del sets
+        torch.cuda.empty_cache()
+    return results
 
 
 def run_e2e(args, mode, layers, sets, world, dev, group, barrier, fused):
@@ -365,8 +554,8 @@ def run_e2e(args, mode, layers, sets, world, dev, group, barrier, fused):
     return f0.elapsed_time(f1), e2e_steps, h2d_bytes, d2h_bytes
 
 
-def finish(args, cfg, mode, layers, sets, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
-           h2d_bytes, d2h_bytes, launches_per_call, clocks):
+def finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
+           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates):
     flops_call = cfg.flops()
     flops_step = flops_call * layers
     value = flops_step * args.steps / (ms_total * 1e-3) / 1e12
@@ -381,6 +570,22 @@ def finish(args, cfg, mode, layers, sets, world, rank, bg, hg, cfg_groups, sub_w
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu_base, _ = cpu_attention_sample(cfg, min(cfg.heads, 8 if cfg.seq <= 8192 else 1), 10.0, 12)
 
+    # The denominator follows the conditions of this run: the burst GEMM figure when the timed region is short
+    # or the SM clock stayed near its maximum, the sustained (power-capped) figure otherwise.
+    timed_s = ms_total * 1e-3
+    near_max = bool(clocks and clocks.get("sm_max_mhz") and clocks["sm_mhz"] >= 0.95 * clocks["sm_max_mhz"])
+    use_burst = timed_s < 2.0 or near_max
+    peak = burst if use_burst else sustained
+    traffic = profiled_traffic_bytes() if (cfg.name == "c2_image1024" and world == 1 and mode == "local") else None
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "frac_of_burst": achieved / burst, "frac_of_sustained": achieved / sustained,
+                "peak_burst": burst, "peak_sustained": sustained,
+                "peak_source": f"{src} {'burst' if use_burst else 'sustained'} bf16 GEMM: timed region {timed_s:.2f} s, "
+                               f"median SM clock {clocks['sm_mhz'] if clocks else 'n/a'} MHz",
+                "kernel": "attn_fwd_kernel", "flops_per_launch": flops_launch, "traffic": traffic,
+                "traffic_source": None if traffic is None else
+                "ncu capture of this kernel on this workload, read from the summary committed under profiles/ "
+                "(not measured in this run)"}
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -393,26 +598,21 @@ def finish(args, cfg, mode, layers, sets, world, rank, bg, hg, cfg_groups, sub_w
                                 "ulysses": f"cfg{cfg_groups} x ulysses{sub_world} ({'peer-store exchange fused into the kernels' if args.transport == 'p2p' else 'NCCL all-to-all'})",
                                 "ring": f"ring{world} ({'copy-engine pulls of K/V shards' if args.transport == 'p2p' else 'NCCL send/recv rotation'})"}[mode],
                 "l2": "inputs larger than L2: every layer call reads its own q/k/v buffers "
-                      f"({layers} sets, {3 * sets[0][0].numel() * 2 / 1e6:.0f} MB each per rank)",
+                      f"({sets_info[0]} sets, {sets_info[1]:.0f} MB each per rank)",
                 "inputs": "N(0,1) q,k,v with unit-weight qk-RMSNorm, bf16, trailing text padding 0-300 keys per batch element",
             },
             "pct_of_peak": {"of_measured_sustained": 100 * value / (sustained * world),
                             "of_measured_burst": 100 * value / (burst * world),
                             "of_nominal_2250": 100 * value / (2250.0 * world)},
-            # the kernel is timed inside seconds-long back-to-back steps under the power cap, so the
-            # sustained GEMM figure is the denominator; the fraction of the burst figure is given beside it
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": sustained, "unit": "TFLOP/s",
-                         "frac": achieved / sustained, "frac_of_burst": achieved / burst, "peak_burst": burst,
-                         "peak_source": f"{src} sustained bf16 GEMM (kernel timed inside a long step)",
-                         "kernel": "attn_fwd_kernel", "flops_per_launch": flops_launch,
-                         "traffic": NCU_TRAFFIC_BYTES_C2 if cfg.name == "c2_image1024" and world == 1 else None},
+            "roofline": roofline,
             "e2e": None if e2e_ms is None else {
                     "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
-                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps, "h2d_gbs_per_rank": h2d_rates,
                     "how": "pinned host q,k,v -> device (double buffered, copy streams) -> dtb200.attention -> pinned host o"},
             "gpu_launches": args.steps * layers * launches_per_call,
             "clocks": clocks,
             "cpu_baseline": cpu_base,
+            "workloads": workloads,
         }
         print(json.dumps(line))
 
@@ -475,6 +675,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cfg-halves", action="store_true", help="ulysses: one sub-group of ranks per batch element")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-workloads", action="store_true",
+                    help="skip the collective placements on the long shapes (the workloads entry of the line)")
     ap.add_argument("--kernel", default="attention", choices=["attention", "prepass"],
                     help="attention (the metric's kernel) or the HBM-bound q/k pre-pass in front of it")
     args = ap.parse_args()

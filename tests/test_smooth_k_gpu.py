@@ -92,7 +92,9 @@ def test_bounded_logit_rows_far_below_the_bound_are_not_flushed():
         dtb200.check_device_status(DEV)
         err = (out.float().cpu() - ref).abs()
         assert out[0, 0, 7].abs().max().item() > 0.0        # the row along -u is a real average of v, not zeros
-        assert err.max().item() <= MAX_ABS_TOL and err.mean().item() <= MEAN_ABS_TOL, (err.max().item(), err.mean().item())
+        # query rows of norm 100 make the softmax pick single value rows, so outputs reach magnitudes of 2-4 where
+        # bf16 steps are 0.016-0.03: the max-abs bound is doubled for this stress case, the mean bound is not
+        assert err.max().item() <= 2 * MAX_ABS_TOL and err.mean().item() <= MEAN_ABS_TOL, (err.max().item(), err.mean().item())
     # smoothed keys make every row's largest logit non-negative: the property the wide gate rests on
     ks = dtb200.smooth_k(kd)
     logits = torch.einsum("bhqd,bhkd->bhqk", qd.float(), ks.float())
