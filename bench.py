@@ -279,8 +279,19 @@ def run_ours(args, cfg):
         else:
             parallel.ring_attention(q, k, v, kv_len=kv_len, out=o)
 
+    balanced = False
+    if mode == "local":
+        # does the automatic mode balance the last wave of this rank's launch (a sweep kernel + a merge kernel)?
+        import ctypes
+
+        from dtb200 import _lib, ops
+
+        q0, k0, v0, n0, o0 = sets[0]
+        probe = ops._fill_params(q0, k0, v0, o0, n0, None, None, 0, 0, None)
+        balanced = _lib.load().dtb_attn_workspace_bytes(ctypes.byref(probe)) > 0
+        launches_per_call = 2 if balanced else 1
     if args.fixed_m:
-        launches_per_call = 4  # two row-norm reductions, the operand kernel, the attention kernel
+        launches_per_call += 3  # two row-norm reductions and the operand kernel in front of the attention kernel
     if mode == "ring":
         launches_per_call = world + 1  # one residual kernel per ring step and the final normalisation
     launches_per_call *= world         # every rank launches its own
@@ -341,7 +352,7 @@ def run_ours(args, cfg):
     if not args.no_workloads and args.workload == "c2_image1024" and mode == "local":
         workloads = run_workloads(args, world, rank, local, dev)
     finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
-           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates)
+           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates, balanced)
     if world > 1:
         dist.destroy_process_group()
 
@@ -555,7 +566,7 @@ def run_e2e(args, mode, layers, sets, world, dev, group, barrier, fused):
 
 
 def finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
-           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates):
+           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates, balanced=False):
     flops_call = cfg.flops()
     flops_step = flops_call * layers
     value = flops_step * args.steps / (ms_total * 1e-3) / 1e12
@@ -594,6 +605,7 @@ def finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, 
             "config": {
                 "workload": cfg.name, "B": cfg.batch, "H": cfg.heads, "S": cfg.seq, "D": cfg.head_dim,
                 "layer_calls_per_step": layers, "softmax": "bounded-logit (fixed-m)" if args.fixed_m else "online",
+                "last_wave": "cut into equal runs of key tiles and merged" if balanced else "whole query blocks",
                 "parallelism": {"local": f"cfg{bg}xheads{hg} (resident head-parallel shards, no collective)",
                                 "ulysses": f"cfg{cfg_groups} x ulysses{sub_world} ({'peer-store exchange fused into the kernels' if args.transport == 'p2p' else 'NCCL all-to-all'})",
                                 "ring": f"ring{world} ({'copy-engine pulls of K/V shards' if args.transport == 'p2p' else 'NCCL send/recv rotation'})"}[mode],

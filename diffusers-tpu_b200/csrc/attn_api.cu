@@ -62,6 +62,98 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------
+// Merge of a balanced launch: the units of the last wave were swept in pieces, whose (o, m, l) lie in
+// consecutive scratch slots per unit (256 rows each).  One warp per query row; lane i owns columns 4i..4i+3.
+// ---------------------------------------------------------------------------
+struct PeerOut {                     // sequence-sharded output of a head-parallel call (shard_rows == 0: none)
+  __nv_bfloat16* o_peer[8];
+  int shard_rows, total_heads, head_offset;
+};
+
+struct PieceMerge {
+  int first_unit;                    // unit index of tail unit 0
+  int n_units;                       // tail units
+  int q_blocks;
+  uint16_t slot_base[148];           // first slot of tail unit x
+  uint8_t slot_count[148];           // its number of slots (0: the unit was swept whole, nothing to merge)
+};
+
+__global__ void __launch_bounds__(256) merge_pieces_kernel(const __grid_constant__ PieceMerge pm,
+                                                           const __grid_constant__ PeerOut po,
+                                                           const float* __restrict__ acc_o, const float* __restrict__ acc_m,
+                                                           const float* __restrict__ acc_l, int Hq, int Sq,
+                                                           __nv_bfloat16* __restrict__ o, int64_t osb, int64_t osh,
+                                                           int64_t oss, const int32_t* __restrict__ kv_len,
+                                                           int zero_padded_rows) {
+  constexpr int kRows = kQTiles * kBlockM;
+  const int x = blockIdx.x / (kRows / 8);
+  const int r = (blockIdx.x % (kRows / 8)) * 8 + (threadIdx.x >> 5);
+  const int count = pm.slot_count[x];
+  if (count == 0) return;
+  const int lane = threadIdx.x & 31;
+  // everything above is independent of the sweep kernel; its results are needed from here on
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int unit = pm.first_unit + x;
+  const int qb = unit % pm.q_blocks;
+  const int bh = unit / pm.q_blocks;
+  const int h = bh % Hq, b = bh / Hq;
+  const int s = qb * kRows + r;
+  if (s >= Sq) return;
+  const int64_t row0 = static_cast<int64_t>(pm.slot_base[x]) * kRows + r;
+  // Pieces are taken four at a time with all their loads issued before any is used: the kernel is bound by
+  // the latency of these loads, not by their volume.
+  float m_max = -INFINITY;
+  for (int i0 = 0; i0 < count; i0 += 4) {
+    float l4[4], m4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t rr = row0 + static_cast<int64_t>(min(i0 + u, count - 1)) * kRows;
+      l4[u] = acc_l[rr];
+      m4[u] = acc_m[rr];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + u < count && l4[u] > 0.f) m_max = fmaxf(m_max, m4[u]);
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l_tot = 0.f;
+  for (int i0 = 0; i0 < count; i0 += 4) {
+    float l4[4], m4[4];
+    float4 v4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t rr = row0 + static_cast<int64_t>(min(i0 + u, count - 1)) * kRows;
+      l4[u] = acc_l[rr];
+      m4[u] = acc_m[rr];
+      v4[u] = reinterpret_cast<const float4*>(acc_o + rr * kHeadDim)[lane];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (i0 + u < count && l4[u] > 0.f) {     // a piece with no valid key wrote no o: never touch it
+        const float w = exp2f(m4[u] - m_max);
+        l_tot += l4[u] * w;
+        acc.x += v4[u].x * w;
+        acc.y += v4[u].y * w;
+        acc.z += v4[u].z * w;
+        acc.w += v4[u].w * w;
+      }
+    }
+  }
+  const bool padded = zero_padded_rows && kv_len != nullptr && (s >= kv_len[b]);
+  const float inv = (l_tot > 0.f && !padded) ? 1.0f / l_tot : 0.f;
+  uint2 packed;
+  packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+  packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+  __nv_bfloat16* dst = o + b * osb + h * osh + s * oss;
+  if (po.shard_rows > 0) {
+    const int dest = s / po.shard_rows;
+    dst = po.o_peer[dest] + ((static_cast<int64_t>(b) * po.total_heads + po.head_offset + h) * po.shard_rows +
+                             (s - dest * po.shard_rows)) * kHeadDim;
+  }
+  reinterpret_cast<uint2*>(dst)[lane] = packed;
+}
+
+// ---------------------------------------------------------------------------
 // Max L2 row norm per head of a bf16 [B,H,S,128] tensor (one warp per row),
 // folded into norms[h] with an integer atomic max (norms are non-negative).
 // ---------------------------------------------------------------------------
@@ -175,6 +267,107 @@ int resolve_splits(const dtb_attn_params* p) {
   return std::max(n, 1);
 }
 
+int current_sm_count() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+    return std::min(sms, 148);
+  (void)cudaGetLastError();
+  return kNumSms;   // no device to ask (sizing queries on a machine without one): a B200's count
+}
+
+// ---------------------------------------------------------------------------
+// Balanced launch (the role of the reference's per-shape tile resolution, diffusers_tpu/kernels/block_sizes.py:442-577,
+// resolved from the static shape alone as in diffusers_tpu/kernels/mesh_attention.py:199-216): with one CTA per
+// (batch, head, query block) unit the last wave of a launch leaves SMs idle - a whole sweep long when the units
+// do not fill it.  When that costs a tenth of the sweep or more, the key tiles of the last wave's units are
+// cut into `sms` runs of equal length; a run that crosses a unit boundary becomes two pieces.  Pieces of one unit
+// get consecutive scratch slots and are merged by merge_pieces_kernel.
+// ---------------------------------------------------------------------------
+constexpr int kMinPieceTiles = 4;      // no run shorter than this many key tiles
+// What the balanced form costs an SM beyond its run of key tiles, in key-tile times: a second pipeline fill and
+// drain (a run usually spans two units), the state written instead of the output, and the merge kernel.
+#ifndef DTB_PIECE_OVERHEAD_TILES
+#define DTB_PIECE_OVERHEAD_TILES 13
+#endif
+constexpr int kPieceOverheadTiles = DTB_PIECE_OVERHEAD_TILES;
+
+struct BalancedPlan {
+  bool use = false;
+  int slots = 0;
+  PieceTable table;
+  PieceMerge merge;
+};
+
+void plan_balanced(const dtb_attn_params* p, int sms, BalancedPlan* plan) {
+  plan->use = false;
+  plan->slots = 0;
+  const int qb = q_blocks(p);
+  const long long units = static_cast<long long>(qb) * p->Hq * p->B;
+  const int n = (p->Skv + kBlockN - 1) / kBlockN;
+  if (units > 0x7fffffffLL || n > 65535) return;
+  const int tail = static_cast<int>(units % sms);
+  if (tail == 0) return;
+  const long long tiles = static_cast<long long>(tail) * n;
+  const int runs = static_cast<int>(std::min<long long>(sms, tiles / kMinPieceTiles));
+  if (runs <= tail) return;
+  const long long run_len = (tiles + runs - 1) / runs;
+  if (run_len + kPieceOverheadTiles > n) return;   // the plain launch is as fast or faster
+  struct Piece { int x, tb, te; };
+  Piece pieces[kMaxPieces];
+  int np = 0;
+  for (int i = 0; i < runs; ++i) {
+    long long s0 = tiles * i / runs, s1 = tiles * (i + 1) / runs;
+    while (s0 < s1) {
+      const int x = static_cast<int>(s0 / n);
+      const long long end = std::min<long long>(s1, static_cast<long long>(x + 1) * n);
+      if (np >= kMaxPieces) return;
+      pieces[np++] = {x, static_cast<int>(s0 - static_cast<long long>(x) * n), static_cast<int>(end - static_cast<long long>(x) * n)};
+      s0 = end;
+    }
+  }
+  // slots: consecutive per unit, in the order of the key ranges (pieces are generated in that order)
+  PieceMerge& mg = plan->merge;
+  mg.first_unit = static_cast<int>(units - tail);
+  mg.n_units = tail;
+  mg.q_blocks = qb;
+  for (int x = 0; x < 148; ++x) { mg.slot_base[x] = 0; mg.slot_count[x] = 0; }
+  int slot_of[kMaxPieces];
+  int slots = 0;
+  for (int i = 0; i < np; ++i) {
+    const bool whole = pieces[i].tb == 0 && pieces[i].te == n;
+    if (whole) { slot_of[i] = -1; continue; }
+    if (mg.slot_count[pieces[i].x] == 0) mg.slot_base[pieces[i].x] = static_cast<uint16_t>(slots);
+    if (mg.slot_count[pieces[i].x] == 255) return;
+    mg.slot_count[pieces[i].x]++;
+    slot_of[i] = slots++;
+  }
+  // longest pieces first
+  int order[kMaxPieces];
+  for (int i = 0; i < np; ++i) order[i] = i;
+  std::stable_sort(order, order + np, [&](int a, int b) {
+    return pieces[a].te - pieces[a].tb > pieces[b].te - pieces[b].tb;
+  });
+  PieceTable& tb = plan->table;
+  tb.whole_units = mg.first_unit;
+  tb.n_pieces = np;
+  tb.q_blocks = qb;
+  for (int k = 0; k < np; ++k) {
+    const Piece& pc = pieces[order[k]];
+    tb.unit[k] = mg.first_unit + pc.x;
+    tb.tile_begin[k] = static_cast<uint16_t>(pc.tb);
+    tb.tile_end[k] = static_cast<uint16_t>(pc.te);
+    tb.slot[k] = static_cast<int16_t>(slot_of[order[k]]);
+  }
+  for (int k = np; k < kMaxPieces; ++k) { tb.unit[k] = 0; tb.tile_begin[k] = tb.tile_end[k] = 0; tb.slot[k] = -1; }
+  plan->slots = slots;
+  plan->use = slots > 0;
+}
+
+size_t balanced_workspace_bytes(int slots) {
+  return static_cast<size_t>(slots) * (kQTiles * kBlockM) * (kHeadDim + 2) * sizeof(float);
+}
+
 size_t split_workspace_bytes(const dtb_attn_params* p, int splits) {
   const size_t rows = static_cast<size_t>(splits) * p->B * p->Hq * p->Sq;
   return rows * (kHeadDim + 2) * sizeof(float);
@@ -201,12 +394,16 @@ cudaError_t ensure_kernel_attrs() {
   e = cudaFuncSetAttribute(attn_fwd_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(kSmemBytes));
   if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(attn_fwd_pieces_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kSmemBytes));
+  if (e != cudaSuccess) return e;
   // The register hand-over inside the kernel (setmaxnreg) is sized for kLaunchRegs registers per thread at
   // launch; with any other count a warpgroup could wait for registers that never come.  Refuse to launch then.
-  const void* variants[4] = {reinterpret_cast<const void*>(attn_fwd_kernel<false, false>),
+  const void* variants[5] = {reinterpret_cast<const void*>(attn_fwd_kernel<false, false>),
                              reinterpret_cast<const void*>(attn_fwd_kernel<true, false>),
                              reinterpret_cast<const void*>(attn_fwd_kernel<false, true>),
-                             reinterpret_cast<const void*>(attn_fwd_kernel<true, true>)};
+                             reinterpret_cast<const void*>(attn_fwd_kernel<true, true>),
+                             reinterpret_cast<const void*>(attn_fwd_pieces_kernel)};
   for (const void* fn : variants) {
     cudaFuncAttributes fa;
     e = cudaFuncGetAttributes(&fa, fn);
@@ -264,6 +461,46 @@ int fill_kernel_params(const dtb_attn_params* p, AttnKernelParams* kp) {
   return DTB_OK;
 }
 
+// Sweep with the last wave in pieces, then the merge (see plan_balanced).  `workspace` holds
+// balanced_workspace_bytes(plan.slots) bytes.
+int launch_balanced(const dtb_attn_params* p, AttnKernelParams kp, const BalancedPlan& plan, void* workspace,
+                    cudaStream_t s) {
+  const size_t rows = static_cast<size_t>(plan.slots) * (kQTiles * kBlockM);
+  kp.acc_o = static_cast<float*>(workspace);
+  kp.acc_m = kp.acc_o + rows * kHeadDim;
+  kp.acc_l = kp.acc_m + rows;
+  kp.acc_init = 1;
+  attn_fwd_pieces_kernel<<<dim3(plan.table.whole_units + plan.table.n_pieces), dim3(kNumThreads), kSmemBytes, s>>>(
+      kp, plan.table);
+  if (!launch_ok("attn_fwd_pieces_kernel launch")) return DTB_ERR_LAUNCH;
+  PeerOut po;
+  for (int i = 0; i < 8; ++i) po.o_peer[i] = kp.o_peer[i];
+  po.shard_rows = kp.o_shard_rows;
+  po.total_heads = kp.o_total_heads;
+  po.head_offset = kp.o_head_offset;
+  // The merge is launched as a programmatic dependent of the sweep: its blocks are set up while the sweep
+  // drains and wait (griddepcontrol.wait in the kernel) until all of the sweep's writes are visible.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan.merge.n_units * (kQTiles * kBlockM / 8));
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const float* c_o = kp.acc_o;
+  const float* c_m = kp.acc_m;
+  const float* c_l = kp.acc_l;
+  if (!cuda_ok(cudaLaunchKernelEx(&cfg, merge_pieces_kernel, plan.merge, po, c_o, c_m, c_l, static_cast<int>(p->Hq),
+                                  static_cast<int>(p->Sq), kp.o, kp.o_stride_b, kp.o_stride_h, kp.o_stride_s,
+                                  p->kv_len, kp.zero_padded_rows),
+               "merge_pieces_kernel launch"))
+    return DTB_ERR_LAUNCH;
+  return DTB_OK;
+}
+
 }  // namespace
 }  // namespace dtb
 
@@ -278,6 +515,11 @@ extern "C" int dtb_attn_supported(const dtb_attn_params* p, int* why) {
 
 extern "C" size_t dtb_attn_workspace_bytes(const dtb_attn_params* p) {
   if (check_params(p, false) != DTB_OK) return 0;
+  if (p->num_splits == 0 && !(p->flags & DTB_FLAG_QK_FP8)) {
+    BalancedPlan plan;
+    plan_balanced(p, current_sm_count(), &plan);
+    return plan.use ? balanced_workspace_bytes(plan.slots) : 0;
+  }
   const int splits = resolve_splits(p);
   return splits > 1 ? split_workspace_bytes(p, splits) : 0;
 }
@@ -291,6 +533,20 @@ extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t wo
   st = fill_kernel_params(p, &kp);
   if (st != DTB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (p->num_splits == 0 && !(p->flags & DTB_FLAG_QK_FP8)) {
+    // automatic: one CTA per unit, the last wave balanced over the SMs when that pays and the caller's scratch
+    // holds the pieces (a missing or smaller workspace is not an error: the plain launch runs instead)
+    BalancedPlan plan;
+    plan_balanced(p, current_sm_count(), &plan);
+    if (plan.use) {
+      if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 15u)) return DTB_ERR_ALIGN;
+      if (workspace == nullptr || workspace_bytes < balanced_workspace_bytes(plan.slots)) plan.use = false;
+    }
+    if (plan.use) return launch_balanced(p, kp, plan, workspace, s);
+    attn_fwd_kernel<false, false><<<dim3(q_blocks(p), p->Hq, p->B), dim3(kNumThreads), kSmemBytes, s>>>(kp);
+    return launch_ok("kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;
+  }
 
   int splits = resolve_splits(p);
   if (splits > 1) {
@@ -498,6 +754,13 @@ extern "C" int dtb_attn_fwd_scatter(const dtb_attn_params* p, const dtb_attn_sca
   kp.o_shard_rows = sc->shard_rows;
   kp.o_total_heads = sc->total_heads;
   kp.o_head_offset = sc->head_offset;
+  if (p->num_splits == 0 && sc->workspace != nullptr) {
+    BalancedPlan plan;
+    plan_balanced(p, current_sm_count(), &plan);
+    if (plan.use && (reinterpret_cast<uintptr_t>(sc->workspace) & 15u)) return DTB_ERR_ALIGN;
+    if (plan.use && sc->workspace_bytes >= balanced_workspace_bytes(plan.slots))
+      return launch_balanced(p, kp, plan, sc->workspace, static_cast<cudaStream_t>(stream));
+  }
   attn_fwd_kernel<false, false><<<dim3(q_blocks(p), p->Hq, p->B), dim3(kNumThreads), kSmemBytes,
                            static_cast<cudaStream_t>(stream)>>>(kp);
   return launch_ok("attn_fwd_kernel launch") ? DTB_OK : DTB_ERR_LAUNCH;

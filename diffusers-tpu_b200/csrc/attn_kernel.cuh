@@ -109,6 +109,23 @@ struct AttnKernelParams {
   int table_qblocks, table_width;
 };
 
+// Work list of a balanced launch.  CTAs [0, whole_units) each take one whole (batch, head, query block) unit, in
+// unit order (query block fastest).  The units after those - the last, incomplete wave - are cut into pieces of
+// nearly equal numbers of key tiles: CTA whole_units + i sweeps key tiles [tile_begin[i], tile_end[i]) of unit
+// unit[i] and, unless that is the unit's whole range (slot[i] < 0), leaves its unnormalised (o, m, l) in scratch
+// slot slot[i] for the merge kernel.  Pieces are listed longest first, so the hardware's in-order dispatch of
+// CTAs to freed SMs packs them evenly.
+constexpr int kMaxPieces = 304;
+struct PieceTable {
+  int whole_units;
+  int n_pieces;
+  int q_blocks;                      // query blocks per (batch, head): unit = (b * Hq + h) * q_blocks + qblock
+  int32_t unit[kMaxPieces];
+  uint16_t tile_begin[kMaxPieces];
+  uint16_t tile_end[kMaxPieces];
+  int16_t slot[kMaxPieces];
+};
+
 // Warp-uniform bounded wait: every lane polls, and the warp agrees on the outcome so
 // that warp-collective instructions after it are never reached by a partial warp.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, int site) {
@@ -199,8 +216,11 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
 // ---------------------------------------------------------------------------
 //              kQkFp8 = true    : q and k are E4M3 bytes ([B, H, S, 128] with byte strides); the score MMA runs as
 //                                 kind::f8f6f4 with 32 contraction elements per instruction, P*V stays bf16.
-template <bool kResidual, bool kQkFp8>
-__global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnKernelParams p) {
+//              kTable = true    : the CTA's work comes from a PieceTable (balanced launch); a piece that covers only
+//                                 part of a unit's keys emits its state like a residual call, a whole unit
+//                                 writes the normalised output.
+template <bool kResidual, bool kQkFp8, bool kTable>
+__device__ __forceinline__ void attn_fwd_body(const AttnKernelParams& p, const PieceTable* tb) {
   constexpr uint32_t kQkTileBytes = kQkFp8 ? kPanelBytes : kTileBytes;   // bytes of one 128-row Q or K tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem;
@@ -214,11 +234,30 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int split = blockIdx.z % p.num_splits;
-  const int b = blockIdx.z / p.num_splits;
-  const int h = blockIdx.y;
+  int split = 0, b, h, qblock, piece_begin = 0, piece_end = 0x7fffffff, slot = -1;
+  if (kTable) {
+    const int id = blockIdx.x;
+    int unit_id = id;
+    if (id >= tb->whole_units) {
+      const int i = id - tb->whole_units;
+      unit_id = tb->unit[i];
+      piece_begin = tb->tile_begin[i];
+      piece_end = tb->tile_end[i];
+      slot = tb->slot[i];
+    }
+    qblock = unit_id % tb->q_blocks;
+    const int bh = unit_id / tb->q_blocks;
+    h = bh % p.Hq;
+    b = bh / p.Hq;
+  } else {
+    split = blockIdx.z % p.num_splits;
+    b = blockIdx.z / p.num_splits;
+    h = blockIdx.y;
+    qblock = blockIdx.x;
+  }
   const int hk = h / (p.Hq / p.Hkv);
-  const int q0 = blockIdx.x * (kQTiles * kBlockM);
+  const int q0 = qblock * (kQTiles * kBlockM);
+  const bool emit_state = kResidual || (kTable && slot >= 0);   // leave (o, m, l) instead of the normalised output
 
   // Valid keys of this call: global indices [kv_offset, kv_offset + Skv) below kv_len[b].
   const int kv_len_b = (p.kv_len != nullptr) ? max(p.kv_len[b], 0) : 0x7fffffff;
@@ -229,7 +268,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
   int n_total = (kv_eff + kBlockN - 1) / kBlockN;
   if (p.kv_table != nullptr) {
     const int cls = p.head_class != nullptr ? p.head_class[h] : 0;
-    const int64_t trow = static_cast<int64_t>(cls) * p.table_qblocks + blockIdx.x;
+    const int64_t trow = static_cast<int64_t>(cls) * p.table_qblocks + qblock;
     tile_list = p.kv_table + trow * p.table_width;
     int lo = 0, hi = p.kv_count[trow];
     while (lo < hi) {
@@ -239,19 +278,21 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     n_total = lo;
   }
   const int per_split = (n_total + p.num_splits - 1) / p.num_splits;
-  const int tile_begin = min(split * per_split, n_total);
-  const int tile_end = min(tile_begin + per_split, n_total);
+  const int tile_begin = kTable ? min(piece_begin, n_total) : min(split * per_split, n_total);
+  const int tile_end = kTable ? min(piece_end, n_total) : min(tile_begin + per_split, n_total);
   const int n_tiles = tile_end - tile_begin;
   const bool block_padded = p.zero_padded_rows && (p.q_offset + q0 >= kv_len_b);
 
+  // first row of this CTA's (o, m, l) rows in the state arrays, minus q0 (so that + row addresses them)
   const int64_t unit = kResidual ? ((static_cast<int64_t>(split) * p.B + b) * p.Hq + h) : 0;
+  const int64_t acc_base = kTable ? static_cast<int64_t>(slot) * (kQTiles * kBlockM) - q0 : unit * p.Sq;
 
   if (n_tiles <= 0 || block_padded) {
     // Nothing to attend to: emit zeros (normal) or the empty state (residual, when initialising).
     if (threadIdx.x < kNumSoftmaxThreads) {
       const int row = q0 + threadIdx.x;
       if (row < p.Sq) {
-        if (!kResidual) {
+        if (!emit_state) {
           uint4* dst;
           if (p.o_shard_rows > 0) {
             const int dest = row / p.o_shard_rows;
@@ -264,11 +305,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
           for (int i = 0; i < kHeadDim * 2 / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
         } else if (p.acc_init) {
-          float4* dst = reinterpret_cast<float4*>(p.acc_o + (unit * p.Sq + row) * kHeadDim);
+          float4* dst = reinterpret_cast<float4*>(p.acc_o + (acc_base + row) * kHeadDim);
 #pragma unroll
           for (int i = 0; i < kHeadDim / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-          p.acc_m[unit * p.Sq + row] = -INFINITY;
-          p.acc_l[unit * p.Sq + row] = 0.f;
+          p.acc_m[acc_base + row] = -INFINITY;
+          p.acc_l[acc_base + row] = 0.f;
         }
       }
     }
@@ -436,7 +477,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     const uint32_t o_tmem = tmem_base + lane_off + (kQTiles + t) * kBlockN;
     const float scale_log2 = p.scale_log2;
     const bool row_in_range = row < p.Sq;
-    const int64_t acc_row = unit * p.Sq + row;
+    const int64_t acc_row = acc_base + row;
     const uint32_t bar_p_lo = smem_u32(&bars->p_lo[t]);
     const uint32_t bar_p_hi = smem_u32(&bars->p_hi[t]);
 
@@ -522,7 +563,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     if (ok) ok = warp_wait(&bars->o_full[t], 0, ctx, SITE_O_FULL + t);
     if (ok) {
       tc_fence_after();
-      if (kResidual) {
+      if (emit_state) {
         float4* dst = reinterpret_cast<float4*>(p.acc_o + acc_row * kHeadDim);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -603,6 +644,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_c
     __syncthreads();
   }
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+template <bool kResidual, bool kQkFp8>
+__global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnKernelParams p) {
+  attn_fwd_body<kResidual, kQkFp8, false>(p, nullptr);
+}
+
+// The balanced launch of the plain bf16 forward: a 1-D grid of whole units followed by the pieces of `tb`.
+__global__ void __launch_bounds__(kNumThreads, 1) attn_fwd_pieces_kernel(const __grid_constant__ AttnKernelParams p,
+                                                                         const __grid_constant__ PieceTable tb) {
+  attn_fwd_body<false, false, true>(p, &tb);
 }
 
 }  // namespace dtb

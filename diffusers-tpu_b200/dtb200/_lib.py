@@ -65,6 +65,7 @@ class AttnScatter(ctypes.Structure):
     _fields_ = [
         ("out_ptrs", ctypes.c_void_p * 8), ("n_peers", ctypes.c_int32), ("shard_rows", ctypes.c_int32),
         ("head_offset", ctypes.c_int32), ("total_heads", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
     ]
 
 

@@ -119,8 +119,11 @@ class UlyssesP2P:
             yq, yk, yv = self.y
             kv_len_t = ops._kv_len_tensor(kv_len, self.B, dev)
             flags = _lib.FLAG_ZERO_PADDED_ROWS if kv_len_t is not None else 0
-            p = ops._fill_params(yq, yk, yv, None, kv_len_t, None, scale, flags, 1, ops._status_buffer(dev))
+            p = ops._fill_params(yq, yk, yv, None, kv_len_t, None, scale, flags, 0, ops._status_buffer(dev))
             sc = _lib.AttnScatter()
+            ws = ops._workspace(dev, lib.dtb_attn_workspace_bytes(ctypes.byref(p)))   # lets the last wave be balanced
+            if ws is not None:
+                sc.workspace, sc.workspace_bytes = ws.data_ptr(), ws.numel()
             for r in range(self.P):
                 sc.out_ptrs[r] = self.arena.ptr(r, self.o_off)
             sc.n_peers, sc.shard_rows = self.P, self.Sl

@@ -57,7 +57,9 @@ typedef struct dtb_attn_params {
   const float* mk;       /* [2, Hq] bounded-logit operand: row 0 = integral bound m, row 1 = eligibility; NULL = online softmax */
   float scale;           /* softmax scale; <= 0 means 1/sqrt(D) */
   uint32_t flags;        /* DTB_FLAG_* */
-  int32_t num_splits;    /* split-KV factor: 0 = choose automatically, 1 = none, n > 1 = force (needs workspace) */
+  int32_t num_splits;    /* 0 = automatic: one CTA per query block, the last wave of the launch cut into equal runs of key
+                            tiles when its query blocks would leave SMs idle (uses workspace when given); 1 = no splitting;
+                            n > 1 = every query block's keys split n ways (needs workspace) */
   int32_t* status;       /* optional [4] int32 device status words written when a bounded wait runs out; must be zeroed by the caller */
 } dtb_attn_params;
 
@@ -81,6 +83,8 @@ typedef struct dtb_attn_scatter {
   int32_t shard_rows;
   int32_t head_offset;
   int32_t total_heads;
+  void* workspace;        /* optional scratch of dtb_attn_workspace_bytes(p) bytes (device, 16-byte aligned): lets an */
+  size_t workspace_bytes; /* automatic call (p->num_splits == 0) balance its last wave; NULL / 0 = plain launch      */
 } dtb_attn_scatter;
 
 /* Sequence shards -> head shards for up to three tensors at once (q, k, v): this rank's bf16
@@ -130,7 +134,8 @@ const char* dtb_last_error_detail(void);
  * receives the status that dtb_attn_fwd would return. */
 int dtb_attn_supported(const dtb_attn_params* p, int* why);
 
-/* Scratch bytes needed by dtb_attn_fwd for `p` (0 unless split-KV is in effect). */
+/* Scratch bytes dtb_attn_fwd can use for `p` (0 when no form of key splitting applies).  In automatic mode a
+ * missing or smaller workspace is not an error: the call runs unsplit. */
 size_t dtb_attn_workspace_bytes(const dtb_attn_params* p);
 
 /* Normalised joint attention forward: o = softmax(scale * q k^T + key_mask) v.

@@ -136,3 +136,27 @@ def test_smooth_k_argument_validation():
     assert lib.dtb_smooth_k(ctypes.byref(sp), None) == 3
     assert lib.dtb_fixed_m_from_norms(None, None, 4, 4, ctypes.c_float(0.0), None, None) == 1
     assert lib.dtb_fixed_m_from_norms(4096, 4096, 4, 3, ctypes.c_float(0.0), 4096, None) == 3
+
+
+def _shape(B, H, S):
+    p = _params(B=B, Hq=H, Hkv=H, Sq=S, Skv=S, num_splits=0)
+    p.q_stride_h = p.k_stride_h = p.v_stride_h = p.o_stride_h = S * 128
+    p.q_stride_b = p.k_stride_b = p.v_stride_b = p.o_stride_b = H * S * 128
+    return p
+
+
+def test_balanced_launch_is_planned_from_the_static_shape():
+    """Automatic mode cuts the last wave of a launch into equal runs of key tiles only where that beats the plain
+    launch: the scratch request (one 256-row state per piece) says which shapes those are on a 148-SM part."""
+    lib = _lib.load()
+    slot = 256 * (128 + 2) * 4
+    full_c2 = lib.dtb_attn_workspace_bytes(ctypes.byref(_shape(2, 24, 4608)))          # 864 units: 5.84 waves, runs too long to pay
+    quarter_c2 = lib.dtb_attn_workspace_bytes(ctypes.byref(_shape(1, 12, 4608)))       # 216 units: a 68-unit last wave
+    eighth_c2 = lib.dtb_attn_workspace_bytes(ctypes.byref(_shape(1, 6, 4608)))         # 108 units of 36 tiles: runs of 27 do not pay
+    eighth_c3 = lib.dtb_attn_workspace_bytes(ctypes.byref(_shape(1, 6, 16896)))        # 396 units of 132 tiles
+    exact = lib.dtb_attn_workspace_bytes(ctypes.byref(_shape(1, 37, 1024)))            # 148 units: one full wave
+    assert full_c2 == 0 and eighth_c2 == 0 and exact == 0
+    for need in (quarter_c2, eighth_c3):
+        assert need > 0 and need % slot == 0 and need // slot <= 2 * 148
+    # forced modes keep their meaning
+    assert lib.dtb_attn_workspace_bytes(ctypes.byref(_params(Sq=128, Skv=8192, num_splits=1))) == 0
