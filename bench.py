@@ -220,7 +220,9 @@ def run_ours(args, cfg):
     layers = args.layers or LAYERS[cfg.name]
     from dtb200 import parallel
 
-    bg, hg = parallel.placement(cfg.batch, cfg.heads, world) if mode == "local" else (1, 1)
+    # --shard-of N on one GPU: time rank 0's resident shard of an N-GPU placement (what one rank of that run computes)
+    place_world = args.shard_of if (args.shard_of and world == 1 and mode == "local") else world
+    bg, hg = parallel.placement(cfg.batch, cfg.heads, place_world) if mode == "local" else (1, 1)
     b_local = cfg.batch // bg
     h_local = cfg.heads // hg
     my_b = (rank // hg) * b_local
@@ -349,7 +351,7 @@ def run_ours(args, cfg):
     sets.clear()
     torch.cuda.empty_cache()
     workloads = None
-    if not args.no_workloads and args.workload == "c2_image1024" and mode == "local":
+    if not args.no_workloads and args.workload == "c2_image1024" and mode == "local" and not args.shard_of:
         workloads = run_workloads(args, world, rank, local, dev)
     finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
            h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates, balanced)
@@ -567,7 +569,7 @@ def run_e2e(args, mode, layers, sets, world, dev, group, barrier, fused):
 
 def finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
            h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates, balanced=False):
-    flops_call = cfg.flops()
+    flops_call = cfg.flops() / (bg * hg) * world if (args.shard_of and world == 1) else cfg.flops()
     flops_step = flops_call * layers
     value = flops_step * args.steps / (ms_total * 1e-3) / 1e12
     e2e_value = flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12 if e2e_ms else None
@@ -672,6 +674,48 @@ def run_prepass(args, cfg):
     }))
 
 
+def run_smooth_k(args, cfg):
+    """HBM-bound k-smoothing (column means over the valid rows, then subtract and zero the pads) on the workload's
+    key tensor: GB/s against the copy peak.  Algorithmic bytes: K read by each of the two passes and written once."""
+    import dtb200
+
+    dev = torch.device("cuda", 0)
+    B, S, H = cfg.batch, cfg.seq, cfg.heads
+    n_sets = max(2, min(8, int(1.5e9 // (B * S * H * 256))))      # rotate buffers larger than L2
+    g = torch.Generator(device="cuda").manual_seed(0)
+    ks = [torch.randn(B, H, S, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(n_sets)]
+    outs = [torch.empty_like(k) for k in ks]
+    kv_len = torch.full((B,), S - 100, dtype=torch.int32, device=dev)
+    call = lambda i: dtb200.smooth_k(ks[i % n_sets], kv_len=kv_len, out=outs[i % n_sets], want_norms=True)
+    for i in range(max(args.warmup, 3) * n_sets):
+        call(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = args.steps * n_sets
+    e0.record()
+    for i in range(n):
+        call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    algo_bytes = 3 * B * S * H * 256
+    hbm = 6549.1
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        hbm = float(json.load(open(path))["hbm_gbs"])
+    gbs = algo_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "smooth_k_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms * n_sets, "ms_per_call": ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg.name + " k-smoothing", "B": B, "S": S, "H": H, "D": 128,
+                   "l2": f"{n_sets} rotating key tensors of {B * S * H * 256 / 1e6:.0f} MB"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                     "algorithmic_bytes_per_launch": algo_bytes, "kernel": "k_colsum_kernel + k_smooth_kernel",
+                     "traffic": None},
+        "gpu_launches": 2 * n,
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -687,10 +731,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cfg-halves", action="store_true", help="ulysses: one sub-group of ranks per batch element")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="one GPU only: run rank 0's shard of an N-GPU resident placement (kernel studies)")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the collective placements on the long shapes (the workloads entry of the line)")
-    ap.add_argument("--kernel", default="attention", choices=["attention", "prepass"],
-                    help="attention (the metric's kernel) or the HBM-bound q/k pre-pass in front of it")
+    ap.add_argument("--kernel", default="attention", choices=["attention", "prepass", "smooth_k"],
+                    help="attention (the metric's kernel) or one of the HBM-bound kernels in front of it")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -701,6 +747,8 @@ def main():
         run_reference(args, cfg)
     elif args.kernel == "prepass":
         run_prepass(args, cfg)
+    elif args.kernel == "smooth_k":
+        run_smooth_k(args, cfg)
     else:
         run_ours(args, cfg)
 

@@ -50,7 +50,21 @@ __global__ void __launch_bounds__(256) k_colsum_kernel(const __grid_constant__ S
   const int r1 = min(r0 + p.rows_per_chunk, n_valid);
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   const __nv_bfloat16* base = p.k + b * p.sb + h * p.sh;
-  for (int r = r0 + rg; r < r1; r += 16) {
+  // four rows in flight per thread: the kernel lives on memory-level parallelism
+  int r = r0 + rg;
+  for (; r + 48 < r1; r += 64) {
+    uint4 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) raw[u] = reinterpret_cast<const uint4*>(base + (r + 16 * u) * p.ss)[hl];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float x[8];
+      unpack8(raw[u], x);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += x[i];
+    }
+  }
+  for (; r < r1; r += 16) {
     float x[8];
     unpack8(reinterpret_cast<const uint4*>(base + r * p.ss)[hl], x);
 #pragma unroll
@@ -93,12 +107,13 @@ __global__ void __launch_bounds__(256) k_smooth_kernel(const __grid_constant__ S
   // the sixteen lanes of a row run the same number of steps; the other half of the warp may run one fewer,
   // so the row reduction names only its own half
   const uint32_t half_mask = 0xffffu << (threadIdx.x & 16);
-  for (int r = r0 + rg; r < r1; r += 16) {
+  // two rows per step, both loads issued before either row is worked on
+  auto finish_row = [&](int r, const uint4& raw, bool live) {
     uint4 packed = make_uint4(0u, 0u, 0u, 0u);
     float n2 = 0.f;
-    if (r < n_valid) {
+    if (live) {
       float x[8];
-      unpack8(reinterpret_cast<const uint4*>(src + r * p.ss)[hl], x);
+      unpack8(raw, x);
       uint32_t y[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) y[i] = pack_bf16x2(x[2 * i] - mean[2 * i], x[2 * i + 1] - mean[2 * i + 1]);
@@ -112,6 +127,16 @@ __global__ void __launch_bounds__(256) k_smooth_kernel(const __grid_constant__ S
     for (int o = 8; o > 0; o >>= 1) n2 += __shfl_xor_sync(half_mask, n2, o);
     best = fmaxf(best, n2);
     reinterpret_cast<uint4*>(dst + r * p.os)[hl] = packed;
+  };
+  for (int r = r0 + rg; r < r1; r += 32) {
+    const int rb = r + 16;
+    const bool has_b = rb < r1;                      // the same for the sixteen lanes of a row
+    const bool live_a = r < n_valid, live_b = has_b && rb < n_valid;
+    uint4 raw_a = make_uint4(0u, 0u, 0u, 0u), raw_b = raw_a;
+    if (live_a) raw_a = reinterpret_cast<const uint4*>(src + r * p.ss)[hl];
+    if (live_b) raw_b = reinterpret_cast<const uint4*>(src + rb * p.ss)[hl];
+    finish_row(r, raw_a, live_a);
+    if (has_b) finish_row(rb, raw_b, live_b);
   }
   if (p.norm_max != nullptr) {
     if (hl == 0 && best > 0.f) atomicMax(&max_s, __float_as_int(sqrtf(best)));
