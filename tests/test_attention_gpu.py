@@ -64,6 +64,27 @@ def test_config1_full_call_matches_both_oracles():
     assert err.max().item() <= MAX_ABS_TOL and err.mean().item() <= MEAN_ABS_TOL
 
 
+@pytest.mark.parametrize("use_fixed_m", [False, True])
+def test_restated_reference_kernel_agrees_on_config2_heads(use_fixed_m):
+    """Three heads of one C2 batch element at full length (4608 tokens, 36 key tiles, its own padding) against the
+    step-by-step restatement of the reference kernel (bf16 rounding of the scaled query, exp2, bf16 P, the
+    reference's 1024/2048 tiling, online or per-head constant offset): the two are different tilings of the same
+    arithmetic and must agree within the path's tolerance, as each does with the fp32 oracle."""
+    cfg = CONFIGS["c2_image1024"]
+    q, k, v, kv_len = make_inputs(cfg, 11, heads=3)
+    q, k, v = q[1:2], k[1:2], v[1:2]
+    n = int(kv_len[1])
+    assert n < cfg.seq
+    out = dtb200.attention(q.to(DEV), k.to(DEV), v.to(DEV), kv_len=[n], use_fixed_m=use_fixed_m)
+    dtb200.check_device_status(DEV)
+    restated = O.attention_restated(q, k, v, kv_len=n, use_fixed_m=use_fixed_m).float()
+    err = (out.float().cpu()[:, :, :n] - restated[:, :, :n]).abs()
+    assert err.max().item() <= MAX_ABS_TOL and err.mean().item() <= MEAN_ABS_TOL, (err.max().item(), err.mean().item())
+    fp32 = O.attention_fp32(q, k, v, kv_len=[n])
+    err = (restated[:, :, :n] - fp32[:, :, :n]).abs()
+    assert err.max().item() <= MAX_ABS_TOL and err.mean().item() <= MEAN_ABS_TOL
+
+
 @pytest.mark.parametrize("call_index", [0, 7, 59])
 def test_config2_sampled_rows(call_index):
     cfg = CONFIGS["c2_image1024"]
