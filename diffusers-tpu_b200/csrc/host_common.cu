@@ -87,6 +87,30 @@ int encode_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_
 }
 }  // namespace
 
+int make_tmap_rows_bf16(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t row_stride,
+                        int box_rows, int box_cols) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) {
+    snprintf(g_detail, sizeof(g_detail), "cuTensorMapEncodeTiled entry point not found");
+    return DTB_ERR_LAUNCH;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || ((row_stride * 2) & 15)) return DTB_ERR_ALIGN;
+  if (rows <= 0 || cols <= 0 || row_stride < cols || box_cols > 64 || box_rows > 256) return DTB_ERR_SHAPE;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstr[1] = {static_cast<cuuint64_t>(row_stride * 2)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_detail, sizeof(g_detail), "cuTensorMapEncodeTiled (2-D) failed with CUresult %d (rows=%lld cols=%lld)",
+             static_cast<int>(r), static_cast<long long>(rows), static_cast<long long>(cols));
+    return DTB_ERR_LAUNCH;
+  }
+  return DTB_OK;
+}
+
 bool device_is_sm100() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return false;

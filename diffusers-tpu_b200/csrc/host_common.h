@@ -29,6 +29,11 @@ int make_tmap_bhsd(CUtensorMap* out, const void* base, int64_t B, int64_t H, int
 int make_tmap_bhsd_u8(CUtensorMap* out, const void* base, int64_t B, int64_t H, int64_t S, int64_t sb, int64_t sh,
                       int64_t ss, int box_rows);
 
+// Tensor map over a row-major bf16 matrix [rows, cols] (row stride in elements): boxes of `box_cols` (<= 64)
+// columns x `box_rows` rows, 128-byte swizzle, zero fill outside the matrix.
+int make_tmap_rows_bf16(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t row_stride,
+                        int box_rows, int box_cols);
+
 // Records the CUDA error behind a DTB_ERR_LAUNCH so that dtb_last_error_detail() can name it.
 // Returns true when `e` is cudaSuccess.
 bool cuda_ok(cudaError_t e, const char* what);

@@ -15,7 +15,7 @@ CSRC_DIR = os.path.join(os.path.dirname(PKG_DIR), "csrc")
 INCLUDE_DIR = os.path.join(os.path.dirname(os.path.dirname(PKG_DIR)), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libdtb200_attn.so")
 
-SOURCES = ["host_common.cu", "selftest.cu", "attn_api.cu", "prepass.cu", "smooth_k.cu"]
+SOURCES = ["host_common.cu", "selftest.cu", "attn_api.cu", "prepass.cu", "smooth_k.cu", "out_proj.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

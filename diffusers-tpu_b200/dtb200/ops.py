@@ -534,6 +534,61 @@ def qk_prepass(
     return outs[0], outs[1], (outs[2] if value is not None else None), mk
 
 
+def _out_proj_params(o: torch.Tensor, w: torch.Tensor) -> _lib.OutProjParams:
+    if not o.is_cuda or not w.is_cuda:
+        raise RuntimeError("out_proj needs CUDA tensors: dtb200 has no CPU path")
+    if o.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise NotImplementedError("out_proj takes bfloat16 operands")
+    if o.dim() != 4 or o.shape[-1] != 128:
+        raise NotImplementedError(f"attention output must be [B, heads, seq, 128], got {tuple(o.shape)}")
+    if w.dim() != 2 or w.shape[0] != o.shape[1] * 128 or w.shape[1] % 8:
+        raise ValueError(f"weight must be [heads * 128 = {o.shape[1] * 128}, N] with N a multiple of 8, got {tuple(w.shape)}")
+    p = _lib.OutProjParams()
+    p.o = o.data_ptr()
+    p.o_stride_b, p.o_stride_h, p.o_stride_s = o.stride()[:3]
+    p.w, p.w_stride_k = w.data_ptr(), w.stride(0)
+    p.B, p.H_local, p.S, p.D, p.N = o.shape[0], o.shape[1], o.shape[2], 128, w.shape[1]
+    p.status = _status_buffer(o.device).data_ptr()
+    return p
+
+
+def out_proj(o: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y[b, s, :] = sum_h o[b, h, s, :] @ w[h*128:(h+1)*128, :]``: the ``to_out`` projection applied to the
+    attention output in its ``[B, heads, seq, 128]`` layout (no heads -> channels transpose), bf16 ``[B, seq, N]``.
+
+    With head-sharded attention output (``diffusers_tpu/models/minimax_h3/jax_image_pipeline.py:574-593``) ``w`` holds
+    the rows of the weight that belong to the local heads and the result is this GPU's partial sum; see
+    :func:`out_proj_reduce_` for the form that adds it straight into the owners' buffers."""
+    o, w = _dense_last(o), (w if (w.stride(1) == 1 and w.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0) else w.contiguous())
+    p = _out_proj_params(o, w)
+    if out is None:
+        out = torch.empty(o.shape[0], o.shape[2], w.shape[1], dtype=torch.bfloat16, device=o.device)
+    p.out = out.data_ptr()
+    p.out_stride_b, p.out_stride_s = out.stride()[:2]
+    p.n_dest = 0
+    with torch.cuda.device(o.device):
+        st = _lib.load().dtb_out_proj(ctypes.byref(p), _stream_ptr(o.device))
+    _lib.check(st, "dtb_out_proj")
+    return out
+
+
+def out_proj_reduce_(o: torch.Tensor, w: torch.Tensor, dest_ptrs: Sequence[int], rows_per_dest: int) -> None:
+    """Adds this GPU's partial sums of the projection (f32) into the buffers that own the rows: row ``b * seq + s`` of
+    the flattened result goes to ``dest_ptrs[row // rows_per_dest]``, a contiguous f32 ``[rows_per_dest, N]`` buffer
+    given by its device address (this GPU's or a peer's mapped into this process).  The buffers must already hold
+    what the sums are added to (zeros, a bias, the residual) and the caller orders the ranks around the call."""
+    o, w = _dense_last(o), (w if (w.stride(1) == 1 and w.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0) else w.contiguous())
+    p = _out_proj_params(o, w)
+    if not 1 <= len(dest_ptrs) <= 8:
+        raise ValueError("1 to 8 destination buffers")
+    for i, ptr in enumerate(dest_ptrs):
+        p.red_dst[i] = int(ptr)
+    p.n_dest, p.rows_per_dest = len(dest_ptrs), int(rows_per_dest)
+    with torch.cuda.device(o.device):
+        st = _lib.load().dtb_out_proj(ctypes.byref(p), _stream_ptr(o.device))
+    _lib.check(st, "dtb_out_proj")
+
+
 class BlockTable:
     """Device-resident block-sparsity table at the kernel's granularity (256 query rows x 128 keys).
 

@@ -231,6 +231,33 @@ int dtb_smooth_k(const dtb_smooth_k_params* sp, void* stream);
 int dtb_fixed_m_from_norms(const float* q_norms, const float* k_norms, int32_t Hq, int32_t Hkv, float gate,
                            float* mk_out, void* stream);
 
+/* Output projection behind head-sharded attention output: y[b, s, :] (+)= sum over the local heads h of
+ * o[b, h, s, :] . w[h * 128 : (h + 1) * 128, :], bf16 operands, f32 accumulation.  o is the attention output in its
+ * [B, H_local, S, 128] layout (element strides given), w the H_local * 128 rows of the projection weight that belong
+ * to these heads ([K, N] row-major, row stride w_stride_k), N a multiple of 8.
+ *   n_dest == 0: y is written as bf16 [B, S, N] (out, element strides out_stride_b / out_stride_s).
+ *   n_dest  > 0: the f32 partial sums are added (vector reductions, order not fixed) into red_dst[g / rows_per_dest],
+ *                a contiguous f32 [rows_per_dest, N] buffer that may live on another GPU, at row g % rows_per_dest,
+ *                where g = b * S + s: the reduce-scatter half of the all-reduce over head shards, fused into the
+ *                kernel.  The buffers must hold zeros (or the bias / residual to add to) before the first
+ *                contribution arrives, and the caller synchronises the ranks around the call. */
+typedef struct dtb_out_proj_params {
+  const void* o;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  const void* w;
+  int64_t w_stride_k;
+  void* out;
+  int64_t out_stride_b, out_stride_s;
+  void* red_dst[8];
+  int32_t n_dest, rows_per_dest;
+  int32_t B, H_local, S, D, N;
+  int32_t* status;       /* optional [4] int32 device status words, as in dtb_attn_params */
+} dtb_out_proj_params;
+
+/* Replaces the `to_out` linear that follows keep-heads attention and the all-reduce XLA inserts behind it
+ * (diffusers_tpu/models/minimax_h3/jax_image_pipeline.py:574-593). */
+int dtb_out_proj(const dtb_out_proj_params* pp, void* stream);
+
 /* Saturating E4M3 cast of a bf16 [B, H, S, 128] tensor, x * mult clamped to +-448, written contiguously; feeds the
  * DTB_FLAG_QK_FP8 variant of dtb_attn_fwd.  Replaces diffusers_tpu/kernels/fp8_cast.py:28-39 `quantize_saturating` as
  * applied to q and k in diffusers_tpu/kernels/splash.py:420-424. */

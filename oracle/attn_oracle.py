@@ -278,3 +278,12 @@ def qk_prepass(q: torch.Tensor, k: torch.Tensor, v: Optional[torch.Tensor] = Non
         outs = [torch.where(keep, t, torch.zeros((), dtype=t.dtype)) for t in outs]
     outs = [t.transpose(1, 2).contiguous() for t in outs]
     return (outs[0], outs[1], outs[2] if v is not None else None)
+
+
+def out_proj(o: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``to_out`` behind head-major attention output: f32 ``[B, S, N]`` from ``o`` ``[B, H, S, D]`` and the ``[H*D, N]``
+    rows of the weight for those heads; a partial sum when the heads are a shard
+    (diffusers_tpu/models/minimax_h3/jax_image_pipeline.py:574-593)."""
+    B, H, S, D = o.shape
+    x = o.detach().cpu().float().permute(0, 2, 1, 3).reshape(B, S, H * D)
+    return x @ w.detach().cpu().float()
