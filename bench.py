@@ -532,6 +532,41 @@ def run_workloads(args, world, rank, local, dev):
             torch.cuda.empty_cache()
         del sets
         torch.cuda.empty_cache()
+    # ---- the projection behind keep-heads attention on the C2 shapes: GEMM with the reduce-scatter over the head
+    # shards fused into its epilogue (peer reductions) against GEMM + NCCL reduce-scatter
+    cfg = CONFIGS["c2_image1024"]
+    if world > 1 and cfg.heads % world == 0 and (cfg.batch * cfg.seq) % world == 0:
+        from dtb200 import symm
+
+        B, S, H, N = cfg.batch, cfg.seq, cfg.heads, cfg.heads * 128
+        Hl = H // world
+        g = torch.Generator(device=dev).manual_seed(900 + rank)
+        n_sets = 4
+        os_ = [torch.randn(B, Hl, S, 128, generator=g, device=dev).to(torch.bfloat16) for _ in range(n_sets)]
+        w_local = (torch.randn(Hl * 128, N, generator=g, device=dev) * (H * 128) ** -0.5).to(torch.bfloat16)
+        flops = 2.0 * B * S * (H * 128) * N
+        rows = B * S // world
+        op = symm.OutProjReduceScatter(B, S, N, device=dev)
+        op_exact = symm.OutProjReduceScatter(B, S, N, device=dev, exact=True)
+        part = torch.empty(B, S, N, dtype=torch.bfloat16, device=dev)
+        shard = torch.empty(rows, N, dtype=torch.bfloat16, device=dev)
+
+        def nccl_call(o):
+            dtb200.out_proj(o, w_local, out=part)
+            dist.reduce_scatter_tensor(shard, part.view(B * S, N))
+
+        nvlink_bytes = (world - 1) / world * B * S * N * 4            # f32 partial sums that leave this GPU
+        for name, fn, how in (("p2p", lambda o: op(o, w_local), "bf16 partial rows stored into the owners' staging slots by the GEMM's epilogue, summed there"),
+                              ("p2p_f32_reductions", lambda o: op_exact(o, w_local), "f32 partial sums added into the owners' shards by the GEMM's epilogue"),
+                              ("nccl", nccl_call, "bf16 GEMM, then NCCL reduce-scatter of the bf16 partial sums")):
+            ms, clk = _timed_calls(fn, os_, 3, 20, world, rank, local, dev)
+            dtb200.check_device_status(dev)
+            results[f"c2_image1024_out_proj/reduce_scatter{world}/{name}"] = {
+                "ms_per_call": ms, "tflops": flops / (ms * 1e-3) / 1e12, "n_gpus_used": world,
+                "sm_mhz": clk["sm_mhz"] if clk else None, "parallelism": f"head shards x {world}: {how}",
+                "nvlink_gbs_per_gpu": (nvlink_bytes if "f32" in name else nvlink_bytes / 2) / (ms * 1e-3) / 1e9,
+                "frac_of_nvlink_770": (nvlink_bytes if "f32" in name else nvlink_bytes / 2) / (ms * 1e-3) / 1e9 / 770.0}
+        del op, op_exact
     return results
 
 
@@ -752,6 +787,47 @@ def run_smooth_k(args, cfg):
     }))
 
 
+def run_out_proj(args, cfg):
+    """The projection behind the attention call on the workload's shapes (all heads on one GPU, N = heads * 128):
+    TFLOP/s (2 * B * S * K * N per call) against the measured bf16 GEMM peak."""
+    import dtb200
+
+    dev = torch.device("cuda", 0)
+    B, S, H = cfg.batch, cfg.seq, cfg.heads
+    N = H * 128
+    n_sets = max(2, min(8, int(1.0e9 // (B * S * H * 256))))
+    g = torch.Generator(device="cuda").manual_seed(0)
+    os_ = [torch.randn(B, H, S, 128, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(n_sets)]
+    w = (torch.randn(H * 128, N, generator=g, device=dev, dtype=torch.float32) * (H * 128) ** -0.5).to(torch.bfloat16)
+    outs = [torch.empty(B, S, N, dtype=torch.bfloat16, device=dev) for _ in range(n_sets)]
+    call = lambda i: dtb200.out_proj(os_[i % n_sets], w, out=outs[i % n_sets])
+    for i in range(max(args.warmup, 3) * n_sets):
+        call(i)
+    torch.cuda.synchronize()
+    dtb200.check_device_status(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = args.steps * n_sets
+    e0.record()
+    for i in range(n):
+        call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    flops = 2.0 * B * S * (H * 128) * N
+    burst, sustained, src = measured_peaks()
+    tf = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "out_proj_tflops", "value": tf, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms * n_sets, "ms_per_call": ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg.name + " output projection", "B": B, "S": S, "K": H * 128, "N": N,
+                   "l2": f"{n_sets} rotating attention outputs of {B * S * H * 256 / 1e6:.0f} MB"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": burst, "unit": UNIT, "frac": tf / burst,
+                     "peak_source": f"{src} burst bf16 GEMM", "flops_per_launch": flops, "kernel": "out_proj_kernel",
+                     "traffic": None},
+        "gpu_launches": n,
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -772,8 +848,8 @@ def main():
     ap.add_argument("--no-bounded", action="store_true", help="skip the bounded-logit (fixed-m) figure beside the headline")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the collective placements on the long shapes (the workloads entry of the line)")
-    ap.add_argument("--kernel", default="attention", choices=["attention", "prepass", "smooth_k"],
-                    help="attention (the metric's kernel) or one of the HBM-bound kernels in front of it")
+    ap.add_argument("--kernel", default="attention", choices=["attention", "prepass", "smooth_k", "out_proj"],
+                    help="attention (the metric's kernel), one of the HBM-bound kernels in front of it, or the projection behind it")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -786,6 +862,8 @@ def main():
         run_prepass(args, cfg)
     elif args.kernel == "smooth_k":
         run_smooth_k(args, cfg)
+    elif args.kernel == "out_proj":
+        run_out_proj(args, cfg)
     else:
         run_ours(args, cfg)
 

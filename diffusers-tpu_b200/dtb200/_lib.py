@@ -28,7 +28,7 @@ EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
     "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_attn_fwd_sparse", "dtb_scatter_heads",
     "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands", "dtb_qk_prepass", "dtb_quantize_e4m3",
-    "dtb_smooth_k", "dtb_smooth_k_scratch_bytes", "dtb_fixed_m_from_norms", "dtb_out_proj",
+    "dtb_smooth_k", "dtb_smooth_k_scratch_bytes", "dtb_fixed_m_from_norms", "dtb_out_proj", "dtb_sum_partials",
     "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_wait_timeout",
 )
 
@@ -129,6 +129,7 @@ class OutProjParams(ctypes.Structure):
         ("w", ctypes.c_void_p), ("w_stride_k", ctypes.c_int64),
         ("out", ctypes.c_void_p), ("out_stride_b", ctypes.c_int64), ("out_stride_s", ctypes.c_int64),
         ("red_dst", ctypes.c_void_p * 8), ("n_dest", ctypes.c_int32), ("rows_per_dest", ctypes.c_int32),
+        ("partials", ctypes.c_int32), ("src_rank", ctypes.c_int32),
         ("B", ctypes.c_int32), ("H_local", ctypes.c_int32), ("S", ctypes.c_int32), ("D", ctypes.c_int32),
         ("N", ctypes.c_int32), ("status", ctypes.c_void_p),
     ]
@@ -178,6 +179,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         lib.dtb_smooth_k_scratch_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32]
         lib.dtb_fixed_m_from_norms.restype = ctypes.c_int
         lib.dtb_fixed_m_from_norms.argtypes = [vp, vp, ctypes.c_int32, ctypes.c_int32, ctypes.c_float, vp, vp]
+        lib.dtb_sum_partials.restype = ctypes.c_int
+        lib.dtb_sum_partials.argtypes = [vp, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp, vp]
         lib.dtb_out_proj.restype = ctypes.c_int
         lib.dtb_out_proj.argtypes = [ctypes.POINTER(OutProjParams), vp]
         lib.dtb_qk_prepass.restype = ctypes.c_int

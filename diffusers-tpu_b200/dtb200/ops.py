@@ -572,11 +572,16 @@ def out_proj(o: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = 
     return out
 
 
-def out_proj_reduce_(o: torch.Tensor, w: torch.Tensor, dest_ptrs: Sequence[int], rows_per_dest: int) -> None:
-    """Adds this GPU's partial sums of the projection (f32) into the buffers that own the rows: row ``b * seq + s`` of
-    the flattened result goes to ``dest_ptrs[row // rows_per_dest]``, a contiguous f32 ``[rows_per_dest, N]`` buffer
-    given by its device address (this GPU's or a peer's mapped into this process).  The buffers must already hold
-    what the sums are added to (zeros, a bias, the residual) and the caller orders the ranks around the call."""
+def out_proj_reduce_(o: torch.Tensor, w: torch.Tensor, dest_ptrs: Sequence[int], rows_per_dest: int, *,
+                     partials_from: Optional[int] = None) -> None:
+    """Sends this GPU's partial projection to the buffers that own the rows: row ``b * seq + s`` of the flattened
+    result goes to ``dest_ptrs[row // rows_per_dest]``, given by its device address (this GPU's or a peer's mapped
+    into this process).
+
+    ``partials_from=r``: bf16 rows stored into slot ``r`` of the destination's staging buffer, bf16
+    ``[n_src, rows_per_dest, N]``, for :func:`sum_partials` on the owner.  ``partials_from=None``: f32 sums added by
+    vector reductions into the destination's f32 ``[rows_per_dest, N]`` buffer, which must already hold what they are
+    added to (zeros, a bias, the residual).  The caller orders the ranks around the call."""
     o, w = _dense_last(o), (w if (w.stride(1) == 1 and w.data_ptr() % 16 == 0 and w.stride(0) % 8 == 0) else w.contiguous())
     p = _out_proj_params(o, w)
     if not 1 <= len(dest_ptrs) <= 8:
@@ -584,9 +589,24 @@ def out_proj_reduce_(o: torch.Tensor, w: torch.Tensor, dest_ptrs: Sequence[int],
     for i, ptr in enumerate(dest_ptrs):
         p.red_dst[i] = int(ptr)
     p.n_dest, p.rows_per_dest = len(dest_ptrs), int(rows_per_dest)
+    if partials_from is not None:
+        p.partials, p.src_rank = 1, int(partials_from)
     with torch.cuda.device(o.device):
         st = _lib.load().dtb_out_proj(ctypes.byref(p), _stream_ptr(o.device))
     _lib.check(st, "dtb_out_proj")
+
+
+def sum_partials(staged: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 ``[rows, N]`` sum (f32 accumulation, slot order) of the staged partial projections ``[n_src, rows, N]``."""
+    if not staged.is_cuda or staged.dtype != torch.bfloat16 or staged.dim() != 3 or not staged.is_contiguous():
+        raise NotImplementedError("sum_partials takes a contiguous CUDA bf16 [n_src, rows, N] tensor")
+    n_src, rows, N = staged.shape
+    if out is None:
+        out = torch.empty(rows, N, dtype=torch.bfloat16, device=staged.device)
+    with torch.cuda.device(staged.device):
+        st = _lib.load().dtb_sum_partials(staged.data_ptr(), n_src, rows, N, out.data_ptr(), _stream_ptr(staged.device))
+    _lib.check(st, "dtb_sum_partials")
+    return out
 
 
 class BlockTable:

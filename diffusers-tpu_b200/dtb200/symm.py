@@ -233,3 +233,55 @@ class RingPull:
         if self.P > 1:
             self.arena.barrier(1)        # nobody still pulls from a shard that the next call republishes
         return res
+
+
+class OutProjReduceScatter:
+    """``to_out`` behind head-sharded attention output, with the reduce-scatter over the head shards done by the GEMM.
+
+    Every rank multiplies its own heads' attention output ``[B, H/P, S, 128]`` (read in place, no transpose) by its rows
+    of the projection weight and sends each finished tile straight to the rank that owns those rows, so the transfer
+    over NVLink runs under the GEMM.  This is the all-reduce that follows keep-heads attention in
+    ``diffusers_tpu/models/minimax_h3/jax_image_pipeline.py:574-593`` up to its all-gather half: each rank ends up
+    with rows ``[rank * B*S/P, (rank + 1) * B*S/P)`` of the projected stream.
+
+    ``exact=False`` (default): bf16 partial rows stored into the owner's staging slot for the sending rank, summed
+    there in f32 - the same bytes on the wire as a bf16 reduce-scatter; returns bf16.  ``exact=True``: f32 partial sums
+    added into the owner's shard by vector reductions (twice the bytes, atomics over NVLink); returns f32.
+    """
+
+    def __init__(self, batch: int, seq: int, n_out: int, group=None, device: Optional[torch.device] = None,
+                 exact: bool = False):
+        self.P = dist.get_world_size(group)
+        if self.P > 8:
+            raise ValueError("at most 8 peers")
+        rows = batch * seq
+        if rows % self.P:
+            raise ValueError(f"{rows} rows do not divide over {self.P} ranks")
+        self.B, self.S, self.N, self.rows, self.exact = batch, seq, n_out, rows // self.P, exact
+        nbytes = self.rows * n_out * (4 if exact else 2 * self.P)
+        self.arena = SymmArena(nbytes + 4096, group, device)
+        self.rank = self.arena.rank
+        self.off = self.arena.carve(nbytes)
+        if exact:
+            self.acc = self.arena.local(self.off, (self.rows, n_out), torch.float32)
+        else:
+            self.staged = self.arena.local(self.off, (self.P, self.rows, n_out), torch.bfloat16)
+            self.result = torch.empty(self.rows, n_out, dtype=torch.bfloat16, device=self.arena.device)
+
+    def __call__(self, o_local: torch.Tensor, w_local: torch.Tensor) -> torch.Tensor:
+        """Returns this rank's ``[B*S/P, N]`` row shard of the summed projection (overwritten by the next call)."""
+        dev = self.arena.device
+        if tuple(o_local.shape[::2]) != (self.B, self.S) or w_local.shape[1] != self.N:
+            raise ValueError("shapes do not match the buffers this object was built for")
+        ptrs = [self.arena.ptr(r, self.off) for r in range(self.P)]
+        with torch.cuda.device(dev):
+            if self.exact:
+                self.acc.zero_()
+                self.arena.barrier(0)        # every shard is zero before anybody adds to it
+                ops.out_proj_reduce_(o_local, w_local, ptrs, self.rows)
+                self.arena.barrier(1)        # every rank's contributions to my shard have landed
+                return self.acc
+            self.arena.barrier(0)            # every owner has summed the previous call's slots
+            ops.out_proj_reduce_(o_local, w_local, ptrs, self.rows, partials_from=self.rank)
+            self.arena.barrier(1)            # every rank's rows of my shard have landed
+            return ops.sum_partials(self.staged, out=self.result)

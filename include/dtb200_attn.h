@@ -236,11 +236,14 @@ int dtb_fixed_m_from_norms(const float* q_norms, const float* k_norms, int32_t H
  * [B, H_local, S, 128] layout (element strides given), w the H_local * 128 rows of the projection weight that belong
  * to these heads ([K, N] row-major, row stride w_stride_k), N a multiple of 8.
  *   n_dest == 0: y is written as bf16 [B, S, N] (out, element strides out_stride_b / out_stride_s).
- *   n_dest  > 0: the f32 partial sums are added (vector reductions, order not fixed) into red_dst[g / rows_per_dest],
- *                a contiguous f32 [rows_per_dest, N] buffer that may live on another GPU, at row g % rows_per_dest,
- *                where g = b * S + s: the reduce-scatter half of the all-reduce over head shards, fused into the
- *                kernel.  The buffers must hold zeros (or the bias / residual to add to) before the first
- *                contribution arrives, and the caller synchronises the ranks around the call. */
+ *   n_dest  > 0: the reduce-scatter half of the all-reduce over head shards, fused into the kernel.  Row g = b * S + s
+ *                of the flattened result belongs to destination g / rows_per_dest (a buffer that may live on another
+ *                GPU), local row g % rows_per_dest.
+ *                partials != 0: this rank's bf16 partial rows are stored into slot src_rank of the destination's
+ *                  staging buffer, bf16 [n_src, rows_per_dest, N]; the owner sums the slots with dtb_sum_partials.
+ *                partials == 0: the f32 partial sums are added (vector reductions, order not fixed) into the
+ *                  destination's f32 [rows_per_dest, N] buffer, which must hold zeros (or what to add to) before.
+ *                The caller synchronises the ranks around the call. */
 typedef struct dtb_out_proj_params {
   const void* o;
   int64_t o_stride_b, o_stride_h, o_stride_s;
@@ -250,6 +253,7 @@ typedef struct dtb_out_proj_params {
   int64_t out_stride_b, out_stride_s;
   void* red_dst[8];
   int32_t n_dest, rows_per_dest;
+  int32_t partials, src_rank;
   int32_t B, H_local, S, D, N;
   int32_t* status;       /* optional [4] int32 device status words, as in dtb_attn_params */
 } dtb_out_proj_params;
@@ -257,6 +261,10 @@ typedef struct dtb_out_proj_params {
 /* Replaces the `to_out` linear that follows keep-heads attention and the all-reduce XLA inserts behind it
  * (diffusers_tpu/models/minimax_h3/jax_image_pipeline.py:574-593). */
 int dtb_out_proj(const dtb_out_proj_params* pp, void* stream);
+
+/* out[rows, N] (bf16) = sum over n_src slots of staged[n_src, rows, N] (bf16, f32 accumulation in slot order): the
+ * owner's half of the fused reduce-scatter above.  No counterpart in the reference (XLA's all-reduce does it). */
+int dtb_sum_partials(const void* staged, int32_t n_src, int64_t rows, int32_t N, void* out, void* stream);
 
 /* Saturating E4M3 cast of a bf16 [B, H, S, 128] tensor, x * mult clamped to +-448, written contiguously; feeds the
  * DTB_FLAG_QK_FP8 variant of dtb_attn_fwd.  Replaces diffusers_tpu/kernels/fp8_cast.py:28-39 `quantize_saturating` as

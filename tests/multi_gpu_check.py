@@ -3,7 +3,9 @@
     python -m torch.distributed.run --nproc-per-node N tests/multi_gpu_check.py MODE [S] [H] [B]
 
 MODE: ulysses | ring (NCCL collectives), ulysses-p2p | ring-pull (this library's peer-memory kernels),
-ring-pull-fixed-m (bounded-logit softmax with the ring operand), ring-pull-fp8 (E4M3 q/k + that operand).
+ring-pull-fixed-m (bounded-logit softmax with the ring operand), ring-pull-fp8 (E4M3 q/k + that operand),
+out-proj / out-proj-exact (the projection behind head-sharded attention output with its reduce-scatter fused into
+the GEMM: bf16 partial rows stored to the owners and summed there / f32 reductions into the owners' shards).
 Inputs are generated shard by shard on the GPUs (no rank ever builds the whole tensor on the host); for the
 check every rank gathers the keys and values of two heads and compares a strided sample of its own query rows,
 plus its last rows, with the fp32 oracle.
@@ -37,6 +39,39 @@ def make_shard(B, H, Sl, rank, dev):
     return q, k, v.to(torch.bfloat16)
 
 
+def check_out_proj(mode, S, H, B, rank, world, dev):
+    """Every rank holds H / world heads of an attention output and the matching rows of a [H * 128, H * 128] weight;
+    the fused GEMM + reduce-scatter must leave on each rank its row shard of the full projection (f32)."""
+    from dtb200 import symm
+
+    Hl, N = H // world, H * 128
+    g = torch.Generator(device=dev).manual_seed(77 + rank)
+    o_local = torch.randn(B, Hl, S, 128, generator=g, device=dev).to(torch.bfloat16)
+    gw = torch.Generator(device=dev).manual_seed(5)
+    w = (torch.randn(H * 128, N, generator=gw, device=dev) * (H * 128) ** -0.5).to(torch.bfloat16)
+    exact = mode == "out-proj-exact"
+    op = symm.OutProjReduceScatter(B, S, N, device=dev, exact=exact)
+    for _ in range(2):      # twice: the buffers are reused
+        got = op(o_local, w[rank * Hl * 128:(rank + 1) * Hl * 128]).clone().float()
+    dtb200.check_device_status(dev)
+    parts = [torch.empty_like(o_local) for _ in range(world)]
+    dist.all_gather(parts, o_local)
+    o_all = torch.cat(parts, dim=1)
+    rows = B * S // world
+    ref = O.out_proj(o_all, w).reshape(B * S, N)[rank * rows:(rank + 1) * rows]
+    err = (got.cpu() - ref).abs()
+    scale = max(1.0, ref.abs().max().item())
+    # exact: f32 sums of f32 partials; default: bf16 partial rows (one rounding per contributing rank) and a bf16 result
+    tol = 1e-3 * scale if exact else (world + 1) * 2.0 ** -8 * scale
+    ok = torch.tensor([float(err.max().item() <= tol)], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    print(f"rank {rank}: out-proj S={S} H={H} B={B} max_abs={err.max().item():.3e} (row scale {scale:.2f})", flush=True)
+    if rank == 0:
+        print("PARITY OK" if ok.item() == 1.0 else "PARITY FAILED", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if ok.item() == 1.0 else 1)
+
+
 def main():
     mode = sys.argv[1]
     S = int(sys.argv[2]) if len(sys.argv) > 2 else 2048
@@ -46,6 +81,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
+    if mode in ("out-proj", "out-proj-exact"):
+        return check_out_proj(mode, S, H, B, rank, world, dev)
     assert S % world == 0, "the sequence must divide over the ranks"
     Sl = S // world
     q, k, v = make_shard(B, H, Sl, rank, dev)

@@ -160,3 +160,30 @@ def test_balanced_launch_is_planned_from_the_static_shape():
         assert need > 0 and need % slot == 0 and need // slot <= 2 * 148
     # forced modes keep their meaning
     assert lib.dtb_attn_workspace_bytes(ctypes.byref(_params(Sq=128, Skv=8192, num_splits=1))) == 0
+
+
+def test_out_proj_argument_validation():
+    lib = _lib.load()
+    p = _lib.OutProjParams()
+    assert lib.dtb_out_proj(ctypes.byref(p), None) == 1                       # null operands
+    p.o = p.w = p.out = 4096
+    p.B, p.H_local, p.S, p.D, p.N = 1, 2, 256, 128, 384
+    p.o_stride_s, p.o_stride_h, p.o_stride_b = 128, 256 * 128, 2 * 256 * 128
+    p.w_stride_k, p.out_stride_s, p.out_stride_b = 384, 384, 256 * 384
+    p.N = 100
+    assert lib.dtb_out_proj(ctypes.byref(p), None) == 3                       # N not a multiple of 8
+    p.N = 384
+    p.D = 64
+    assert lib.dtb_out_proj(ctypes.byref(p), None) == 3
+    p.D = 128
+    p.out = 4100
+    assert lib.dtb_out_proj(ctypes.byref(p), None) == 4                       # misaligned output
+    p.out = 4096
+    p.n_dest, p.rows_per_dest = 2, 64                                         # two destinations cannot hold 256 rows
+    p.red_dst[0] = p.red_dst[1] = 4096
+    assert lib.dtb_out_proj(ctypes.byref(p), None) == 3
+    p.rows_per_dest = 128
+    p.red_dst[1] = None
+    assert lib.dtb_out_proj(ctypes.byref(p), None) == 1
+    assert lib.dtb_sum_partials(None, 2, 16, 128, None, None) == 1
+    assert lib.dtb_sum_partials(4096, 9, 16, 128, 4096, None) == 3

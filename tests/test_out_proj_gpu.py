@@ -66,6 +66,29 @@ def test_out_proj_reduce_scatter_with_local_buffers_as_peers():
     assert err.max().item() <= 1e-3 * max(1.0, ref.abs().max().item()), err.max().item()
 
 
+def test_out_proj_partial_rows_and_their_sum_with_local_buffers_as_peers():
+    """The default form of the fused reduce-scatter on one GPU: every rank stores bf16 partial rows into its slot of
+    each owner's staging buffer, and each owner sums its slots."""
+    P, B, H, S, N = 4, 2, 8, 320, 384
+    o, w = _case(B, H, S, N, seed=22)
+    od, wd = o.to(DEV), w.to(DEV)
+    rows = B * S // P
+    staged = [torch.full((P, rows, N), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(P)]
+    Hl = H // P
+    for rank in range(P):
+        dtb200.out_proj_reduce_(od[:, rank * Hl:(rank + 1) * Hl], wd[rank * Hl * 128:(rank + 1) * Hl * 128],
+                                [t.data_ptr() for t in staged], rows, partials_from=rank)
+    got = torch.cat([dtb200.sum_partials(t) for t in staged]).view(B, S, N).float().cpu()
+    dtb200.check_device_status(DEV)
+    assert not torch.isnan(got).any()
+    ref = O.out_proj(o, w)
+    err = (got - ref).abs()
+    assert err.max().item() <= (P + 1) * 2.0 ** -8 * max(1.0, ref.abs().max().item()), err.max().item()
+    # slot r of an owner holds exactly rank r's partial projection of the owner's rows
+    part0 = dtb200.out_proj(od[:, :Hl], wd[:Hl * 128]).view(B * S, N)
+    assert torch.equal(staged[1][0], part0[rows:2 * rows])
+
+
 def test_out_proj_rejects_what_it_cannot_do():
     o, w = _case(1, 2, 128, 128, seed=1)
     with pytest.raises(RuntimeError, match="no CPU path"):

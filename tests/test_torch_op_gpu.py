@@ -59,6 +59,8 @@ def _run_ranks(n, mode, *shape):
     ("ring-pull-fixed-m", ()), ("ring-pull-fp8", ()),
     ("ring-pull", (87824, 5, 1)),            # two of the eight 43,912-row shards of the 351,296-token video shape
     ("ulysses-p2p", (16896, 24, 2)),         # the 2048 x 2048 image shape, 12 heads per rank
+    ("out-proj", (4608, 24, 2)),             # to_out behind keep-heads attention on the 1024 x 1024 image shape
+    ("out-proj-exact", (2048, 8, 2)),
 ])
 def test_two_gpu_drivers(mode, shape):
     """Needs two GPUs; on a one-GPU machine these are skipped and the multi-GPU drivers are covered only by the
@@ -73,6 +75,7 @@ def test_two_gpu_drivers(mode, shape):
     ("ring-pull-fp8", (351296, 5, 1)),
     ("ulysses-p2p", (48872, 40, 2)),         # the 480p video shape: 40 heads -> 5 per rank, ragged 6,109-row shards
     ("ulysses", (16896, 24, 2)),
+    ("out-proj", (4608, 24, 2)),             # 3 heads per rank, 1152 rows of the projected stream each
 ])
 def test_eight_gpu_drivers(mode, shape):
     if torch.cuda.device_count() < 8:
