@@ -631,6 +631,13 @@ def run_e2e(args, mode, layers, sets, world, dev, group, barrier, fused):
     return f0.elapsed_time(f1), e2e_steps, h2d_bytes, d2h_bytes
 
 
+def dtb200_describe(cfg, bg, hg):
+    """The library's one-line account of how it launches one rank's call of this placement."""
+    import dtb200
+
+    return dtb200.describe_launch(cfg.batch // bg, cfg.heads // hg, cfg.seq)
+
+
 def finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
            h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates, balanced=False, bounded=None):
     flops_call = cfg.flops() / (bg * hg) * world if (args.shard_of and world == 1) else cfg.flops()
@@ -671,7 +678,7 @@ def finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, 
             "config": {
                 "workload": cfg.name, "B": cfg.batch, "H": cfg.heads, "S": cfg.seq, "D": cfg.head_dim,
                 "layer_calls_per_step": layers, "softmax": "bounded-logit (fixed-m)" if args.fixed_m else "online",
-                "last_wave": "cut into equal runs of key tiles and merged" if balanced else "whole query blocks",
+                "launch": dtb200_describe(cfg, bg, hg),
                 "parallelism": {"local": f"cfg{bg}xheads{hg} (resident head-parallel shards, no collective)",
                                 "ulysses": f"cfg{cfg_groups} x ulysses{sub_world} ({'peer-store exchange fused into the kernels' if args.transport == 'p2p' else 'NCCL all-to-all'})",
                                 "ring": f"ring{world} ({'copy-engine pulls of K/V shards' if args.transport == 'p2p' else 'NCCL send/recv rotation'})"}[mode],

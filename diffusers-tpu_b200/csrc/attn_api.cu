@@ -524,6 +524,32 @@ extern "C" size_t dtb_attn_workspace_bytes(const dtb_attn_params* p) {
   return splits > 1 ? split_workspace_bytes(p, splits) : 0;
 }
 
+extern "C" int dtb_attn_launch_plan(const dtb_attn_params* p, int32_t sms, dtb_launch_plan* out) {
+  static_assert(DTB_MAX_PIECES == kMaxPieces, "the public plan mirrors the kernel's piece table");
+  int st = check_params(p, false);
+  if (st != DTB_OK) return st;
+  if (out == nullptr) return DTB_ERR_NULL;
+  if (sms < 0 || sms > 148) return DTB_ERR_SHAPE;
+  if (sms == 0) sms = current_sm_count();
+  BalancedPlan plan;
+  if (p->num_splits == 0 && !(p->flags & DTB_FLAG_QK_FP8)) plan_balanced(p, sms, &plan);
+  const long long units = static_cast<long long>(q_blocks(p)) * p->Hq * p->B;
+  out->units = static_cast<int32_t>(units);
+  out->key_tiles = (p->Skv + kBlockN - 1) / kBlockN;
+  out->tail_units = static_cast<int32_t>(units % sms);
+  out->whole_units = plan.use ? plan.table.whole_units : static_cast<int32_t>(units);
+  out->n_pieces = plan.use ? plan.table.n_pieces : 0;
+  out->n_slots = plan.use ? plan.slots : 0;
+  for (int i = 0; i < DTB_MAX_PIECES; ++i) {
+    const bool live = plan.use && i < plan.table.n_pieces;
+    out->unit[i] = live ? plan.table.unit[i] : 0;
+    out->tile_begin[i] = live ? plan.table.tile_begin[i] : 0;
+    out->tile_end[i] = live ? plan.table.tile_end[i] : 0;
+    out->slot[i] = live ? plan.table.slot[i] : -1;
+  }
+  return DTB_OK;
+}
+
 extern "C" int dtb_attn_fwd(const dtb_attn_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   int st = check_params(p, true);
   if (st != DTB_OK) return st;

@@ -16,6 +16,7 @@ from .ops import (  # noqa: F401
     BlockTable,
     make_block_table,
     qk_prepass,
+    describe_launch,
     out_proj,
     out_proj_reduce_,
     sum_partials,
@@ -29,5 +30,5 @@ from .ops import (  # noqa: F401
 
 __all__ = [
     "attention", "residual_attention", "residual_attention_", "finalize_residual", "fixed_m_operands",
-    "sdpa", "qk_prepass", "out_proj", "out_proj_reduce_", "sum_partials", "smooth_k", "quantize_e4m3", "sparse_attention", "make_block_table", "BlockTable", "ResidualState", "check_device_status", "FIXED_M_SAFE_BOUND", "FIXED_M_RING_SAFE_BOUND",
+    "sdpa", "describe_launch", "qk_prepass", "out_proj", "out_proj_reduce_", "sum_partials", "smooth_k", "quantize_e4m3", "sparse_attention", "make_block_table", "BlockTable", "ResidualState", "check_device_status", "FIXED_M_SAFE_BOUND", "FIXED_M_RING_SAFE_BOUND",
 ]

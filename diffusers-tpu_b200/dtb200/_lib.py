@@ -26,7 +26,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 # Every symbol the public header declares; tests check that the library exports all of them.
 EXPORTED_SYMBOLS = (
     "dtb_version", "dtb_status_string", "dtb_last_error_detail", "dtb_attn_supported", "dtb_attn_workspace_bytes",
-    "dtb_attn_fwd", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_attn_fwd_sparse", "dtb_scatter_heads",
+    "dtb_attn_fwd", "dtb_attn_launch_plan", "dtb_attn_fwd_static_scratch", "dtb_attn_fwd_scatter", "dtb_attn_fwd_sparse", "dtb_scatter_heads",
     "dtb_attn_fwd_residual", "dtb_attn_finalize", "dtb_fixed_m_operands", "dtb_qk_prepass", "dtb_quantize_e4m3",
     "dtb_smooth_k", "dtb_smooth_k_scratch_bytes", "dtb_fixed_m_from_norms", "dtb_out_proj", "dtb_sum_partials",
     "dtb_selftest_tmem_roundtrip", "dtb_selftest_qk", "dtb_selftest_pv", "dtb_selftest_wait_timeout",
@@ -120,6 +120,17 @@ class SmoothKParams(ctypes.Structure):
     ]
 
 
+class LaunchPlan(ctypes.Structure):
+    """Mirror of ``dtb_launch_plan``."""
+
+    _fields_ = [
+        ("units", ctypes.c_int32), ("key_tiles", ctypes.c_int32), ("whole_units", ctypes.c_int32),
+        ("tail_units", ctypes.c_int32), ("n_pieces", ctypes.c_int32), ("n_slots", ctypes.c_int32),
+        ("unit", ctypes.c_int32 * 304), ("tile_begin", ctypes.c_uint16 * 304), ("tile_end", ctypes.c_uint16 * 304),
+        ("slot", ctypes.c_int16 * 304),
+    ]
+
+
 class OutProjParams(ctypes.Structure):
     """Mirror of ``dtb_out_proj_params``."""
 
@@ -166,6 +177,8 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         lib.dtb_attn_workspace_bytes.argtypes = [ctypes.POINTER(AttnParams)]
         lib.dtb_attn_fwd.restype = ctypes.c_int
         lib.dtb_attn_fwd.argtypes = [ctypes.POINTER(AttnParams), vp, ctypes.c_size_t, vp]
+        lib.dtb_attn_launch_plan.restype = ctypes.c_int
+        lib.dtb_attn_launch_plan.argtypes = [ctypes.POINTER(AttnParams), ctypes.c_int32, ctypes.POINTER(LaunchPlan)]
         lib.dtb_attn_fwd_static_scratch.restype = ctypes.c_int
         lib.dtb_attn_fwd_static_scratch.argtypes = [ctypes.POINTER(AttnParams), vp]
         lib.dtb_attn_fwd_sparse.restype = ctypes.c_int

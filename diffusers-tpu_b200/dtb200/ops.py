@@ -299,6 +299,29 @@ def attention(
     return out
 
 
+def describe_launch(batch: int, heads: int, seq_q: int, seq_kv: Optional[int] = None, *, sms: int = 0) -> str:
+    """One line saying how the automatic mode launches a call of this shape (the counterpart of the line the reference
+    logs per resolved shape, ``diffusers_tpu/kernels/mesh_attention.py:210-214``).  Needs no GPU."""
+    p = _lib.AttnParams()
+    p.q = p.k = p.v = p.o = 4096          # never dereferenced: the plan depends on the shape alone
+    skv = seq_q if seq_kv is None else seq_kv
+    p.B, p.Hq, p.Hkv, p.Sq, p.Skv, p.D = batch, heads, heads, seq_q, skv, 128
+    p.q_stride_s = p.k_stride_s = p.v_stride_s = p.o_stride_s = 128
+    p.q_stride_h = p.o_stride_h = seq_q * 128
+    p.k_stride_h = p.v_stride_h = skv * 128
+    p.q_stride_b = p.o_stride_b = heads * seq_q * 128
+    p.k_stride_b = p.v_stride_b = heads * skv * 128
+    plan = _lib.LaunchPlan()
+    _lib.check(_lib.load().dtb_attn_launch_plan(ctypes.byref(p), int(sms), ctypes.byref(plan)), "dtb_attn_launch_plan")
+    n_sms = sms or 148
+    head = f"{plan.units} query blocks x {plan.key_tiles} key tiles ({plan.units / n_sms:.2f} waves of {n_sms})"
+    if plan.n_pieces == 0:
+        return head + ": plain launch, one CTA per query block"
+    lens = [plan.tile_end[i] - plan.tile_begin[i] for i in range(plan.n_pieces)]
+    return (head + f": {plan.whole_units} whole, the last {plan.tail_units} cut into {plan.n_pieces} pieces of "
+            f"{min(lens)}-{max(lens)} key tiles ({plan.n_slots} merged through scratch)")
+
+
 class ResidualState:
     """Running ``(o, m, l)`` of a ring: ``o`` f32 ``[B,H,Sq,D]`` unnormalised, ``m``/``l`` f32 ``[B,H,Sq]``.
 

@@ -138,6 +138,25 @@ int dtb_attn_supported(const dtb_attn_params* p, int* why);
  * missing or smaller workspace is not an error: the call runs unsplit. */
 size_t dtb_attn_workspace_bytes(const dtb_attn_params* p);
 
+/* How dtb_attn_fwd would launch the call described by `p` in automatic mode on a GPU with `sms` SMs (0: the current
+ * device's count, or a B200's 148 where there is no device): the first whole_units (batch, head, 256-row query block)
+ * units - numbered query block fastest, then head, then batch - are swept whole, one CTA each; when n_pieces > 0 the
+ * remaining tail_units units are swept in n_pieces pieces, piece i being key tiles [tile_begin[i], tile_end[i]) of unit
+ * unit[i], listed longest first; a piece with slot[i] >= 0 leaves its state in that scratch slot for the merge, and
+ * the slots of one unit are consecutive in key order.  n_pieces == 0 means the plain launch.  The plan depends only
+ * on the static shape; it plays the role of the reference's per-shape tile resolution, which logs one line per
+ * resolved shape (diffusers_tpu/kernels/mesh_attention.py:199-216, diffusers_tpu/kernels/block_sizes.py:442-577). */
+#define DTB_MAX_PIECES 304
+typedef struct dtb_launch_plan {
+  int32_t units, key_tiles, whole_units, tail_units, n_pieces, n_slots;
+  int32_t unit[DTB_MAX_PIECES];
+  uint16_t tile_begin[DTB_MAX_PIECES];
+  uint16_t tile_end[DTB_MAX_PIECES];
+  int16_t slot[DTB_MAX_PIECES];
+} dtb_launch_plan;
+
+int dtb_attn_launch_plan(const dtb_attn_params* p, int32_t sms, dtb_launch_plan* out);
+
 /* Normalised joint attention forward: o = softmax(scale * q k^T + key_mask) v.
  * Replaces diffusers_tpu/kernels/splash.py:566-650 `attention(...)` (and the per-sample loop around it
  * in diffusers_tpu/models/moss_image/jax_dit.py:199-203: kv_len is per batch element here). */

@@ -187,3 +187,54 @@ def test_out_proj_argument_validation():
     assert lib.dtb_out_proj(ctypes.byref(p), None) == 1
     assert lib.dtb_sum_partials(None, 2, 16, 128, None, None) == 1
     assert lib.dtb_sum_partials(4096, 9, 16, 128, 4096, None) == 3
+
+
+@pytest.mark.parametrize("B,H,S,sms", [(1, 12, 4608, 148), (1, 6, 16896, 148), (1, 2, 256, 148), (2, 24, 16896, 148),
+                                       (1, 12, 4608, 132), (1, 5, 48872, 148), (3, 7, 2000, 100)])
+def test_launch_plan_covers_every_key_tile_exactly_once(B, H, S, sms):
+    """The work list of a balanced launch: whole units first, then pieces that tile the key range of every unit of
+    the last wave exactly once, longest first, with consecutive scratch slots per unit in key order."""
+    lib = _lib.load()
+    p = _shape(B, H, S)
+    if (B, H, S) == (1, 2, 256, 148):
+        p = _shape(1, 2, 256)
+        p.Skv = 8192
+    plan = _lib.LaunchPlan()
+    assert lib.dtb_attn_launch_plan(ctypes.byref(p), sms, ctypes.byref(plan)) == 0
+    n = plan.key_tiles
+    assert plan.units == B * H * ((p.Sq + 255) // 256) and plan.tail_units == plan.units % sms
+    if plan.n_pieces == 0:
+        assert plan.whole_units == plan.units and plan.n_slots == 0
+        return
+    assert plan.whole_units == plan.units - plan.tail_units and plan.whole_units % sms == 0
+    pieces = [(plan.unit[i], plan.tile_begin[i], plan.tile_end[i], plan.slot[i]) for i in range(plan.n_pieces)]
+    lens = [te - tb for _, tb, te, _ in pieces]
+    assert lens == sorted(lens, reverse=True) and min(lens) >= 1
+    by_unit = {}
+    for u, tb, te, slot in pieces:
+        assert plan.whole_units <= u < plan.units
+        by_unit.setdefault(u, []).append((tb, te, slot))
+    assert len(by_unit) == plan.tail_units
+    slots_seen = []
+    for u, ps in by_unit.items():
+        ps.sort()
+        assert ps[0][0] == 0 and ps[-1][1] == n
+        for (a0, a1, _), (b0, b1, _) in zip(ps, ps[1:]):
+            assert a1 == b0                                   # no gap, no overlap
+        if len(ps) == 1:
+            assert ps[0][2] == -1                             # swept whole: writes the output itself
+        else:
+            s = [x[2] for x in ps]
+            assert s == list(range(s[0], s[0] + len(s)))      # consecutive slots in key order
+            slots_seen += s
+    assert sorted(slots_seen) == list(range(plan.n_slots))
+    # every SM's share: the runs are equal to within one tile
+    assert max(lens) <= -(-plan.tail_units * n // min(sms, plan.tail_units * n // 4)) 
+    assert lib.dtb_attn_workspace_bytes(ctypes.byref(p)) in (0, plan.n_slots * 256 * 130 * 4) or sms != 148
+
+
+def test_describe_launch_names_the_form():
+    import dtb200
+
+    assert "plain launch" in dtb200.describe_launch(2, 24, 4608)
+    assert "cut into" in dtb200.describe_launch(1, 12, 4608)
