@@ -20,6 +20,7 @@
 // Bound: tensor cores (arithmetic intensity ~ N / 2 FLOP per byte of o at fixed w); with the reduction fused the
 // call is bound by the f32 partial sums crossing NVLink (4 bytes per output element per contributing GPU).
 #include <algorithm>
+#include <atomic>
 
 #include "host_common.h"
 #include "ptx.cuh"
@@ -326,15 +327,15 @@ extern "C" int dtb_out_proj(const dtb_out_proj_params* pp, void* stream) {
   kp.S = pp->S;
   kp.N = pp->N;
   kp.status = pp->status;
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];      // the opt-in shared-memory size is a per-device function attribute
   int dev = 0;
   if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return DTB_ERR_LAUNCH;
-  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+  if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
     if (!cuda_ok(cudaFuncSetAttribute(out_proj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(kProjSmemBytes)),
                  "out_proj_kernel attributes"))
       return DTB_ERR_LAUNCH;
-    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
   }
   const dim3 grid((pp->N + kTileN - 1) / kTileN, (pp->S + kTileM - 1) / kTileM, pp->B);
   out_proj_kernel<<<grid, kProjThreads, kProjSmemBytes, static_cast<cudaStream_t>(stream)>>>(kp);
