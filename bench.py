@@ -354,6 +354,28 @@ def run_ours(args, cfg):
         dtb200.check_device_status(dev)
         bounded = {"ms_total": bounded_ms, "eligible_heads": int(mk_static[1].sum().item()), "heads": int(mk_static.shape[1])}
 
+    # ---- an on-box comparator, not the reference: torch's SDPA on the cuDNN backend over the same buffers, without
+    # the padding mask (it attends all keys, which is the same arithmetic per call), timed like the headline
+    comparator = None
+    if mode == "local" and world == 1 and not args.no_comparator and not args.shard_of:
+        try:
+            from torch.nn.attention import SDPBackend, sdpa_kernel
+
+            with sdpa_kernel(SDPBackend.CUDNN_ATTENTION):
+                for s in sets[:min(len(sets), 6)]:
+                    torch.nn.functional.scaled_dot_product_attention(s[0], s[1], s[2])
+                barrier()
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                c0.record()
+                for _ in range(args.steps):
+                    for s in sets:
+                        torch.nn.functional.scaled_dot_product_attention(s[0], s[1], s[2])
+                c1.record()
+                barrier()
+            comparator = {"ms_total": c0.elapsed_time(c1)}
+        except Exception as e:  # a torch build without the cuDNN backend: say so, the headline does not depend on it
+            comparator = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
     # ---- end to end: pinned host buffers -> device -> kernel -> pinned host result, double buffered
     e2e_ms, e2e_steps, h2d_bytes, d2h_bytes = None, 0, 0, 0
     if not args.no_e2e:
@@ -383,7 +405,7 @@ def run_ours(args, cfg):
     if not args.no_workloads and args.workload == "c2_image1024" and mode == "local" and not args.shard_of:
         workloads = run_workloads(args, world, rank, local, dev)
     finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
-           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates, balanced, bounded)
+           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates, balanced, bounded, comparator)
     if world > 1:
         dist.destroy_process_group()
 
@@ -639,7 +661,8 @@ def dtb200_describe(cfg, bg, hg):
 
 
 def finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, sub_world, ms_total, e2e_ms, e2e_steps,
-           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates, balanced=False, bounded=None):
+           h2d_bytes, d2h_bytes, launches_per_call, clocks, workloads, h2d_rates, balanced=False, bounded=None,
+           comparator=None):
     flops_call = cfg.flops() / (bg * hg) * world if (args.shard_of and world == 1) else cfg.flops()
     flops_step = flops_call * layers
     value = flops_step * args.steps / (ms_total * 1e-3) / 1e12
@@ -704,6 +727,13 @@ def finish(args, cfg, mode, layers, sets_info, world, rank, bg, hg, cfg_groups, 
                 "eligible_heads": f"{bounded['eligible_heads']} of {bounded['heads']}",
                 "how": "same calls, per-head constant softmax offset from a statically calibrated operand (norms of the "
                        "first call, margin 1 log2 unit, gate 106.5 because the keys are not k-smoothed); not the headline"},
+            "comparator": None if comparator is None else comparator if "unavailable" in comparator else {
+                "name": "torch.nn.functional.scaled_dot_product_attention, cuDNN backend (a library kernel on this "
+                        "box, not the reference)",
+                "value": flops_step * args.steps / (comparator["ms_total"] * 1e-3) / 1e12, "unit": UNIT,
+                "ms_per_layer_call": comparator["ms_total"] / (args.steps * layers),
+                "how": "same buffers and call count as the headline, timed right after it in the same process; no "
+                       "padding mask (all keys attended)"},
             "workloads": workloads,
         }
         print(json.dumps(line))
@@ -852,6 +882,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="one GPU only: run rank 0's shard of an N-GPU resident placement (kernel studies)")
+    ap.add_argument("--no-comparator", action="store_true", help="skip the cuDNN SDPA comparator timed beside the headline")
     ap.add_argument("--no-bounded", action="store_true", help="skip the bounded-logit (fixed-m) figure beside the headline")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the collective placements on the long shapes (the workloads entry of the line)")

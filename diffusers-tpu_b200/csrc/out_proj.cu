@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(kProjThreads, DTB_PROJ_CTAS_PER_SM) out_proj_k
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->full[slot]), (kc / kProjStages) & 1, ctx, 20 + slot));
       if (!ok) break;
       tc_fence_after();
-      if (lane == 0) {
+      if (elect_one()) {
         const uint32_t base = smem_u32(smem + slot * kStageBytes);
         const uint64_t a_desc = make_smem_desc_sw128(base, 16, 1024);
         const uint64_t w_desc = make_smem_desc_sw128(base + kABytes, kWPanelBytes, 1024);
