@@ -167,10 +167,14 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
       p1 = ex2(x1);
       acc2 = add_f32x2(acc2, pack_f32x2(p0, p1));
       pk[i] = pack_bf16x2(p0, p1);
+      // The first 32 keys of the half go to tensor memory while the other 32 are exponentiated, which hides half
+      // of the store's latency.  Nothing reads them before the arrive in publish(), so a speculated half that is
+      // thrown away is simply overwritten.
+      if (i == 15) tmem_st16(s_tmem + half * 32, pk);
     }
   };
   auto publish = [&](int half) {
-    tmem_st32(s_tmem + half * 32, pk);
+    tmem_st16(s_tmem + half * 32 + 16, pk + 16);
     tmem_wait_st();
     tc_fence_before();
     mbar_arrive(half == 0 ? bar_p_lo : bar_p_hi);
@@ -210,6 +214,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, f
         return;
       }
       acc2 = pack_f32x2(0.f, 0.f);
+      tmem_wait_st();   // the speculated store has to land before the same columns are written again
     }
     const float mx = row_max();
     const bool grow = mx > m_used + kRescaleThreshold;  // always true while m_used == -inf
