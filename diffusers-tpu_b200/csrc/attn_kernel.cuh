@@ -138,7 +138,8 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, const 
 // The whole S row comes out of tensor memory in one load; the row max uses three-input max; the
 // scale-and-subtract and the row sum run on packed f32 pairs; P goes back to tensor memory in two
 // halves of 64 keys, each published on its own mbarrier so the PV MMA of the first half runs while
-// the second half is still being exponentiated.
+// the second half is still being exponentiated.  Once the rows have an offset, the first half is exponentiated
+// with it before the row max is known (see below): the max then only confirms that the offset can stay.
 // ---------------------------------------------------------------------------
 template <bool kFixedM>
 __device__ __forceinline__ void softmax_tile(uint32_t s_tmem, uint32_t o_tmem, float scale_log2, int valid_cols,
