@@ -365,3 +365,34 @@ def test_concurrent_streams_share_nothing_they_should_not():
                 outs.append(dtb200.attention(qd, kd, vd, num_splits=1))
     dtb200.check_device_status(DEV)
     assert all(torch.equal(o, want) for o in outs)
+
+
+@pytest.mark.parametrize("pattern", ["rising", "late_spike", "mixed_rows"])
+def test_offsets_that_move_after_the_first_tile(pattern):
+    """The kernel exponentiates the first half of a tile with the offset it already has and only then confirms it
+    against the tile's maximum; here the maximum does outgrow the offset (by more than the 2^8 of slack) in later
+    tiles - in every tile, in a single late one, or only for some rows of a warp - so the speculated half must be
+    thrown away, the accumulator rescaled, and the result still match the oracle."""
+    g = torch.Generator().manual_seed(21)
+    S = 1024                                              # 8 key tiles
+    u = torch.randn(128, generator=g)
+    u = u / u.norm()
+    noise = 0.05 * torch.randn(1, 2, S, 128, generator=g)
+    ramp = torch.zeros(S)
+    if pattern == "rising":
+        ramp = torch.linspace(0.0, 80.0, S)               # logits climb ~13 log2 units per tile
+    elif pattern == "late_spike":
+        ramp[700:] = 9.0                                  # one jump inside the sixth tile
+    else:
+        ramp[520:] = 9.0
+    k = ramp[None, None, :, None] * u + noise
+    q = torch.randn(1, 2, 512, 128, generator=g) * 0.3
+    q = q + 10.0 * u
+    if pattern == "mixed_rows":
+        q[:, :, ::3] -= 20.0 * u                          # every third row sees the jump as a drop instead
+    v = torch.randn(1, 2, S, 128, generator=g)
+    q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+    ref = O.attention_fp32(q, k, v)
+    for splits in (1, 2):
+        out = dtb200.attention(q.to(DEV), k.to(DEV), v.to(DEV), num_splits=splits)
+        _check(out, ref)
